@@ -1,0 +1,177 @@
+/*
+ * mako_b200 — C ABI of the B200 (sm_100a) token sampler.
+ *
+ * A drop-in for the token-sampling path of jhanssen/mako: what the reference does one row at a time on the host in
+ * mako::gen::Sampler (src/gen/sampler.hpp:22-45, src/gen/sampler.cpp:9-107) is done here for a batch of rows on the
+ * GPU, with results (candidate sets, token ids) identical to the reference on the same logits, history and
+ * uniforms. Plain C types only; every pointer documented as "device" is a CUDA device pointer of the handle's
+ * device, `stream` is a cudaStream_t passed as void*. No function throws; each returns an mk_status and leaves a
+ * message for mk_last_error() (thread-local) on failure.
+ *
+ * Order of operations on a row (reference: src/gen/sampler.hpp:11, sampler.cpp:20-62):
+ *   logit bias (+=)  ->  allowed-token mask (-inf)  ->  repetition / presence / frequency penalties over the
+ *   token history  ->  temperature  ->  min_p  ->  top_k  ->  top_p  ->  draw by inverse CDF with the caller's u.
+ * Bias and mask have no counterpart in the reference; they act on the logits before the reference pipeline sees
+ * them. A masked token stays excluded whatever the penalties do to it.
+ */
+#ifndef MAKO_B200_H
+#define MAKO_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mk_status {
+    MK_OK = 0,
+    MK_ERR_INVALID_ARGUMENT = 1, /* the reference throws std::invalid_argument (sampler.cpp:11-12) */
+    MK_ERR_CUDA = 2,
+    MK_ERR_UNSUPPORTED = 3,
+    MK_ERR_NO_DEVICE = 4
+} mk_status;
+
+/* Per-row result flags (bit set). */
+#define MK_FLAG_NEAR_CDF_BOUNDARY 0x001u /* u*total within 1e-6*total of a CDF boundary beside the chosen token */
+#define MK_FLAG_GUARD_BAND        0x002u /* a keep/drop decision fell inside the numeric guard band (see DESIGN) */
+#define MK_FLAG_NO_CANDIDATE      0x004u /* nothing finite survived: first argmax returned (sampler.cpp:37-38) */
+#define MK_FLAG_ALL_MASKED        0x008u /* the mask allowed no token of this row */
+#define MK_FLAG_OVERFLOW          0x010u /* more candidates than the handle's capacity: token = -1 */
+#define MK_FLAG_VP_TRUNCATED      0x020u /* vocab-parallel: the nucleus may reach past a shard's top-k list */
+#define MK_FLAG_TIMEOUT           0x040u /* a bounded device-side wait ran out: token = -1 */
+#define MK_FLAG_SECOND_PASS       0x080u /* the row was streamed a second time to settle a guard-band decision */
+
+/* Field for field mako::gen::SamplingParams (src/gen/sampler.hpp:12-20). temperature <= 0 selects greedy. */
+typedef struct mk_sampling_params {
+    float temperature;
+    uint32_t top_k;
+    float top_p;
+    float min_p;
+    float presence_penalty;
+    float frequency_penalty;
+    float repetition_penalty;
+} mk_sampling_params;
+
+/* Sparse logit bias entry; id < 0 marks an unused slot. Ids of one row must be distinct. */
+typedef struct mk_bias {
+    int32_t id;
+    float value;
+} mk_bias;
+
+/* A batch of rows. Row b reads logits + b*ld (n_vocab floats), history + b*history_ld, mask + b*mask_ld (words),
+ * bias + b*n_bias. The fast (bulk-copy) path needs logits 16-byte aligned and ld % 4 == 0; other layouts take a
+ * slower path with identical results. */
+typedef struct mk_rows {
+    const float* logits;         /* device [batch][ld] fp32 — the row Sampler::sample is handed (sampler.hpp:27) */
+    uint64_t ld;
+    uint32_t batch;
+    uint32_t n_vocab;            /* columns held here (the whole vocabulary, or one shard of it) */
+    int32_t id_offset;           /* token id of column 0 (vocab-parallel shards), else 0 */
+    uint32_t n_history;          /* history entries per row when history_len == NULL; <= 65535 */
+    const int32_t* history;      /* device [batch][history_ld] generated-token ids = accept() calls (sampler.cpp:15-18) */
+    uint64_t history_ld;
+    const int32_t* history_len;  /* device [batch] or NULL */
+    const uint32_t* mask;        /* device [batch][mask_ld]; bit id%32 of word id/32 set = allowed; NULL = all */
+    uint64_t mask_ld;
+    const mk_bias* bias;         /* device [batch][n_bias] or NULL */
+    uint32_t n_bias;
+    const mk_sampling_params* params_dev; /* device [batch] per-row parameters, or NULL to use `params` */
+    mk_sampling_params params;
+} mk_rows;
+
+/* Per-row outputs (device). Only token is mandatory. cand_* receive the surviving candidates in draw order. */
+typedef struct mk_sample_out {
+    int32_t* token;     /* [batch] */
+    float* prob;        /* [batch] probability of the chosen token = q / total (float) */
+    uint32_t* flags;    /* [batch] MK_FLAG_* */
+    uint32_t* n_cand;   /* [batch] number of surviving candidates */
+    int32_t* cand_ids;  /* [batch][cand_cap] */
+    float* cand_q;      /* [batch][cand_cap] unnormalised weights q (sampler.cpp:33) */
+    uint32_t cand_cap;
+} mk_sample_out;
+
+typedef struct mk_sampler mk_sampler;
+
+/* Library / build information: "mako_b200 <version> sm_100a". */
+const char* mk_version(void);
+/* Message of the last failure on this thread. */
+const char* mk_last_error(void);
+
+/* Replaces Sampler::Sampler(params, n_vocab, seed) (sampler.cpp:9-13) for a batch: allocates the handle's scratch
+ * (candidate lists) for up to max_batch rows of at most n_vocab columns on `device`. n_vocab == 0 is
+ * MK_ERR_INVALID_ARGUMENT, as the reference throws. Nothing is allocated after this call. */
+int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t max_batch);
+void mk_sampler_destroy(mk_sampler* s);
+
+/* The same checks the reference applies upstream of the sampler (src/server/openai.cpp:316-328): all finite,
+ * temperature 0 or >= 1e-3, repetition_penalty in (0, 100], |presence|, |frequency| <= 100. */
+int mk_check_sampling(const mk_sampling_params* p);
+
+/* Replaces Sampler::sample (sampler.cpp:75-84) for rows->batch rows: u[b] in [0,1) is the uniform the reference
+ * would draw from its generator (r = u * total, sampler.cpp:66). One kernel, one pass over the logits. */
+int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, const mk_sample_out* out,
+                            void* stream);
+
+/* Replaces Sampler::verify (sampler.cpp:86-107) for rows->batch (sequence, position) rows with deterministic
+ * drafts: draft[b] is accepted iff u_accept[b]*total < q(draft); else the draft is removed and a token is drawn
+ * with u_redraw[b]. accepted[b] is 0/1, out->token[b] the returned token. */
+int mk_sampler_verify_batch(mk_sampler* s, const mk_rows* rows, const int32_t* draft, const float* u_accept,
+                            const float* u_redraw, const mk_sample_out* out, int32_t* accepted, void* stream);
+
+/* Rejection sampling against a drafter distribution (generalises Sampler::verify, which is the one-hot case):
+ * rows describe the target logits p; draft_logits [batch][draft_ld] the drafter's q (same history, mask, bias and
+ * parameters). The draft token is drawn from q with u_draft, accepted iff u_accept*q(d) < p(d), else redrawn from
+ * max(0, p - q) with u_resample. */
+int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* draft_logits, uint64_t draft_ld,
+                               const float* u_draft, const float* u_accept, const float* u_resample,
+                               int32_t* draft_token, int32_t* accepted, int32_t* token, uint32_t* flags,
+                               void* stream);
+
+/* The acceptance loop of the reference's speculative round (src/gen/session.cpp:481-496,505) over per-position
+ * results laid out [n_seq][n_pos] (n_pos - 1 drafted positions then the bonus position): n_kept[s] = drafts kept
+ * up to the first rejection, next_token[s] = the replacement at the first rejection, or the bonus position's token
+ * if every draft was kept. */
+int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
+                    int32_t* n_kept, int32_t* next_token, void* stream);
+
+/* Vocab-parallel sampling, step 1 of 2 (no counterpart in the reference, which runs on one device): each shard
+ * writes one record per row — its maximum, its sum of exp((l - max)/T) and its `k` best candidates (<= 64) — of
+ * mk_vp_record_bytes(k) bytes. The caller all-gathers the records of all shards ([n_shards][batch] records,
+ * e.g. ncclAllGather) and calls mk_sampler_vp_merge on every rank (or one). */
+uint32_t mk_vp_record_bytes(uint32_t k);
+int mk_sampler_vp_local(mk_sampler* s, const mk_rows* shard_rows, uint32_t k, void* records, void* stream);
+int mk_sampler_vp_merge(mk_sampler* s, const void* gathered, uint32_t n_shards, uint32_t batch, uint32_t k,
+                        uint32_t n_vocab_total, const mk_sampling_params* params, const float* u,
+                        const mk_sample_out* out, void* stream);
+
+/* Host-buffer form of mk_sampler_sample_batch — what the reference's caller has (Sampler::sample takes a host
+ * row, sampler.hpp:27): every pointer in rows/u/out is a HOST pointer (pinned memory overlaps best); the call
+ * copies inputs to device staging owned by the handle, runs the kernel, copies results back and synchronises. */
+int mk_sampler_sample_host(mk_sampler* s, const mk_rows* host_rows, const float* u, const mk_sample_out* host_out);
+
+/* The reference's own object, one row at a time with its own state: replaces mako::gen::Sampler
+ * (src/gen/sampler.hpp:22-45) call for call. Keeps the parameters, the generated-token history (accept,
+ * sampler.cpp:15-18) and a std::mt19937_64 seeded like the reference's, from which it takes the same uniforms in
+ * the same order: one per sample(), one per verify() plus one more after a rejection, none when greedy. `logits`
+ * may be a host pointer (copied, as the reference's callers hold host rows) or a device pointer (read in place).
+ * include/mako_b200/sampler.hpp wraps these five calls in a C++ class with the reference's signatures. */
+typedef struct mk_row_sampler mk_row_sampler;
+int mk_row_sampler_create(mk_row_sampler** out, const mk_sampling_params* p, uint32_t n_vocab, uint64_t seed,
+                          int device);
+void mk_row_sampler_destroy(mk_row_sampler* r);
+int mk_row_sampler_greedy(const mk_row_sampler* r);
+int mk_row_sampler_accept(mk_row_sampler* r, int32_t token);
+int mk_row_sampler_sample(mk_row_sampler* r, const float* logits, int32_t* token);
+int mk_row_sampler_verify(mk_row_sampler* r, const float* logits, int32_t draft, int32_t* accepted, int32_t* token);
+
+/* Test hook: y[i] = the device's float exponential of x[i] (device pointers), which must equal the host C
+ * library's expf bit for bit (the reference calls std::exp(float), sampler.cpp:33). */
+int mk_debug_expf(const float* x_dev, float* y_dev, uint64_t n, void* stream);
+
+/* Bytes the roofline counts for one row: logits once + history + mask + bias + uniforms + outputs. */
+uint64_t mk_row_bytes(uint32_t n_vocab, uint32_t n_history, int has_mask, uint32_t n_bias, uint32_t n_uniforms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

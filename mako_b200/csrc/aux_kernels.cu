@@ -1,0 +1,443 @@
+// Small kernels around the row pipeline: the merge step of vocab-parallel sampling, the resolution of p/q
+// rejection sampling from two candidate lists, and the acceptance loop of a speculative round.
+#include "row_pipeline.h"
+
+#include "device_expf.cuh"
+#include "ptx.cuh"
+
+#include <cfloat>
+
+namespace mk {
+
+namespace {
+
+constexpr int kMergeThreads = 128;
+constexpr int kMergeCap = 2048; // n_shards * k
+
+__device__ void sort_keys(unsigned long long* keys, uint32_t n2, uint32_t n_threads)
+{
+    for (uint32_t k = 2; k <= n2; k <<= 1) {
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            for (uint32_t i = threadIdx.x; i < n2; i += n_threads) {
+                const uint32_t l = i ^ j;
+                if (l > i) {
+                    const unsigned long long a = keys[i], b = keys[l];
+                    const bool up = (i & k) == 0;
+                    if ((a > b) == up) {
+                        keys[i] = b;
+                        keys[l] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+} // namespace
+
+// One CTA per row. Input: for each shard a record {float max; uint32 n|flags; double sum; (float logit, int32 id) x k}
+// where sum = sum over the shard of exp((l - max) * inv_t) (approximate) and the list holds the shard's k best
+// edited logits by (logit desc, id asc). The merge recomputes exact weights against the global maximum, so a
+// candidate's q is the same float the single-device pipeline computes; only the row total that top_p needs when no
+// other truncation is active comes from the rescaled partial sums, and decisions within 1e-5 of it are flagged.
+__global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeArgs a)
+{
+    __shared__ unsigned long long keys[kMergeCap];
+    __shared__ uint32_t s_n, s_nfinal;
+    __shared__ uint32_t s_shard_in[64];  // entries of each shard that are in the deciding set
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const uint32_t rb = vp_record_bytes(a.k);
+    const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
+    const float inv_t = __fdiv_rn(1.0f, prm.temperature);
+    const bool greedy = prm.temperature <= 0.0f;
+    const float minp_eff = (1.0f < prm.min_p) ? 1.0f : prm.min_p;
+    const float ninf = -__int_as_float(0x7f800000);
+
+    auto rec = [&](uint32_t g) { return a.gathered + ((size_t)g * a.batch + row) * rb; };
+
+    // global maximum and first argmax
+    float m = ninf;
+    uint32_t arg_id = 0;
+    bool any = false, nan0 = false;
+    for (uint32_t g = 0; g < a.n_shards; ++g) {
+        const float mg = *reinterpret_cast<const float*>(rec(g));
+        const uint32_t ng = *reinterpret_cast<const uint32_t*>(rec(g) + 4) & 0xffffu;
+        if (mg != mg) {
+            nan0 = true;
+            continue;
+        }
+        if (ng > 0 && mg > ninf) {
+            const uint2 first = *reinterpret_cast<const uint2*>(rec(g) + kVpHeaderBytes);
+            if (!any || mg > m) { // shards ascend in id, so the first shard holding the maximum wins ties
+                m = mg;
+                arg_id = first.y;
+                any = true;
+            }
+        }
+    }
+    if (nan0) {
+        m = __int_as_float(0x7fc00000);
+        arg_id = 0;
+    }
+    if (tid == 0) {
+        s_n = 0;
+        s_nfinal = 0;
+    }
+    if (tid < 64)
+        s_shard_in[tid] = 0;
+    __syncthreads();
+
+    uint32_t flags = 0;
+    if (greedy) {
+        if (tid == 0) {
+            if (a.token) a.token[row] = (int32_t)arg_id;
+            if (a.prob) a.prob[row] = 1.0f;
+            if (a.flags) a.flags[row] = 0;
+            if (a.n_cand) a.n_cand[row] = 1;
+            if (a.cand_ids && a.cand_cap) a.cand_ids[(size_t)row * a.cand_cap] = (int32_t)arg_id;
+            if (a.cand_q && a.cand_cap) a.cand_q[(size_t)row * a.cand_cap] = 1.0f;
+        }
+        return;
+    }
+
+    // exact weights; key carries the shard in the low bits of a side table (recomputed from id ranges later)
+    if (!nan0) {
+        for (uint32_t e = tid; e < a.n_shards * a.k; e += kMergeThreads) {
+            const uint32_t g = e / a.k, i = e % a.k;
+            const uint32_t ng = *reinterpret_cast<const uint32_t*>(rec(g) + 4) & 0xffffu;
+            if (i >= ng)
+                continue;
+            const uint2 c = reinterpret_cast<const uint2*>(rec(g) + kVpHeaderBytes)[i];
+            const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), inv_t);
+            const float q = expf_host_exact(x);
+            if (q >= minp_eff && q > 0.0f) {
+                const uint32_t slot = atomicAdd(&s_n, 1u);
+                keys[slot] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
+            }
+        }
+    }
+    __syncthreads();
+    uint32_t n = s_n;
+    if (n == 0) {
+        flags |= MK_FLAG_NO_CANDIDATE;
+        if (tid == 0)
+            keys[0] = ((unsigned long long)__float_as_uint(1.0f) << 32) | arg_id;
+        n = 1;
+        __syncthreads();
+    }
+    const bool minp_on = minp_eff > 0.0f;
+    const bool cut_k = prm.top_k > 0 && prm.top_k < n;
+    const bool use_topp = prm.top_p < 1.0f;
+    const bool sorted = cut_k || use_topp;
+    const bool need_sum = use_topp && !minp_on && !(prm.top_k > 0 && prm.top_k < a.n_vocab_total);
+    uint32_t n2 = 2;
+    while (n2 < n)
+        n2 <<= 1;
+    for (uint32_t i = tid; i < n2; i += kMergeThreads) {
+        unsigned long long key = ~0ull;
+        if (i < n) {
+            const unsigned long long raw = keys[i];
+            const uint32_t qb = (uint32_t)(raw >> 32), id = (uint32_t)(raw & 0xffffffffull);
+            key = sorted ? (((unsigned long long)(~qb) << 32) | id) : (((unsigned long long)id << 32) | qb);
+        }
+        keys[i] = key;
+    }
+    __syncthreads();
+    if (n > 1)
+        sort_keys(keys, n2, kMergeThreads);
+
+    if (tid == 0) {
+        auto q_at = [&](uint32_t i) -> float {
+            const unsigned long long key = keys[i];
+            return sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
+        };
+        auto id_at = [&](uint32_t i) -> uint32_t {
+            const unsigned long long key = keys[i];
+            return sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
+        };
+        // A shard whose whole list is inside the deciding set may hold further members the merge cannot see.
+        uint32_t n_decide = n; // the set whose completeness matters: all candidates when the total is their sum
+        if (cut_k)
+            n = prm.top_k;
+        if (use_topp) {
+            double total = 0.0, band;
+            if (need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
+                const double c2 = (double)inv_t * 1.4426950408889634;
+                for (uint32_t g = 0; g < a.n_shards; ++g) {
+                    const float mg = *reinterpret_cast<const float*>(rec(g));
+                    const double sg = *reinterpret_cast<const double*>(rec(g) + 8);
+                    if (mg > ninf && sg > 0.0)
+                        total += sg * exp2((double)(mg - m) * c2);
+                }
+                band = 1e-5 * total;
+            } else {
+                for (uint32_t i = 0; i < n; ++i)
+                    total += (double)q_at(i);
+                band = 0x1p-40 * total;
+            }
+            const double want = (double)prm.top_p * total;
+            double run = 0.0, prev = 0.0;
+            uint32_t k = 0;
+            while (k < n && run < want) {
+                prev = run;
+                run += (double)q_at(k++);
+            }
+            if (need_sum && run < want)
+                flags |= MK_FLAG_VP_TRUNCATED;
+            if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
+                flags |= MK_FLAG_GUARD_BAND;
+            n = max(k, 1u);
+            if (need_sum)
+                n_decide = n;
+        }
+        if (cut_k && !use_topp)
+            n_decide = n;
+        else if (cut_k)
+            n_decide = min(n_decide, prm.top_k);
+        // count members per shard among the deciding set
+        const uint32_t shard_w = (a.n_vocab_total + a.n_shards - 1) / a.n_shards;
+        for (uint32_t i = 0; i < n_decide; ++i) {
+            const uint32_t g = min(id_at(i) / max(shard_w, 1u), a.n_shards - 1);
+            if (g < 64)
+                s_shard_in[g] += 1;
+        }
+        for (uint32_t g = 0; g < a.n_shards && g < 64; ++g) {
+            const uint32_t hdr = *reinterpret_cast<const uint32_t*>(rec(g) + 4);
+            const uint32_t ng = hdr & 0xffffu;
+            const bool more = (hdr & 0x40000000u) != 0;
+            if ((hdr & 0x80000000u) || (more && ng > 0 && s_shard_in[g] >= ng))
+                flags |= MK_FLAG_VP_TRUNCATED;
+        }
+        float total = 0.0f;
+        for (uint32_t i = 0; i < n; ++i)
+            total = __fadd_rn(total, q_at(i));
+        float r = __fmul_rn(a.u[row], total);
+        const float eps = 1e-6f * total;
+        int32_t tok = (int32_t)id_at(n - 1);
+        float prob = __fdiv_rn(q_at(n - 1), total);
+        for (uint32_t i = 0; i < n; ++i) {
+            const float q = q_at(i);
+            if (r < q) {
+                tok = (int32_t)id_at(i);
+                prob = __fdiv_rn(q, total);
+                if ((i > 0 && r < eps) || (i + 1 < n && __fsub_rn(q, r) < eps))
+                    flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                break;
+            }
+            r = __fsub_rn(r, q);
+        }
+        if (a.token) a.token[row] = tok;
+        if (a.prob) a.prob[row] = prob;
+        if (a.flags) a.flags[row] = flags;
+        if (a.n_cand) a.n_cand[row] = n;
+        s_nfinal = n;
+    }
+    __syncthreads();
+    if (a.cand_ids || a.cand_q) {
+        const uint32_t nf = min(s_nfinal, a.cand_cap);
+        for (uint32_t i = tid; i < nf; i += kMergeThreads) {
+            const unsigned long long key = keys[i];
+            const uint32_t id = sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
+            const float q = sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
+            if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)id;
+            if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + i] = q;
+        }
+    }
+}
+
+cudaError_t launch_vp_merge(const VpMergeArgs& a, cudaStream_t stream)
+{
+    if (a.batch == 0)
+        return cudaSuccess;
+    vp_merge_kernel<<<a.batch, kMergeThreads, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+// ---- p/q rejection sampling from two candidate lists ---------------------------------------------------------------
+// One CTA per position. p_* / q_* are the final candidate lists (draw order) of the target and drafter rows with
+// their float totals; draft_token was drawn from q. Accept iff u_accept * q(d) < p(d) on normalised probabilities;
+// otherwise walk max(0, p - q) over the union in ascending id with u_resample.
+namespace {
+constexpr int kPqThreads = 128;
+}
+
+__global__ void __launch_bounds__(kPqThreads) pq_resolve_kernel(const PqResolveArgs a)
+{
+    extern __shared__ unsigned long long pq_keys[]; // [2][cap2]
+    __shared__ float s_pd;
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const uint32_t np = a.p_n[row], nq = a.q_n[row];
+    const uint32_t bad = MK_FLAG_OVERFLOW | MK_FLAG_TIMEOUT;
+    const uint32_t fl = (a.p_flags[row] | a.q_flags[row]);
+    if ((fl & bad) || np > a.cap || nq > a.cap) {
+        if (tid == 0) {
+            a.accepted[row] = 0;
+            a.token[row] = -1;
+            if (a.flags) a.flags[row] = fl | MK_FLAG_OVERFLOW;
+        }
+        return;
+    }
+    uint32_t cap2 = 2;
+    while (cap2 < a.cap)
+        cap2 <<= 1;
+    unsigned long long* kp = pq_keys;
+    unsigned long long* kq = pq_keys + cap2;
+    const int32_t d = a.draft_token[row];
+    if (tid == 0)
+        s_pd = 0.0f;
+    __syncthreads();
+    const float total_p = a.p_total[row], total_q = a.q_total[row];
+    uint32_t n2p = 2, n2q = 2;
+    while (n2p < np) n2p <<= 1;
+    while (n2q < nq) n2q <<= 1;
+    for (uint32_t i = tid; i < n2p; i += kPqThreads) {
+        unsigned long long key = ~0ull;
+        if (i < np) {
+            const int32_t id = a.p_ids[(size_t)row * a.cap + i];
+            const float q = a.p_q[(size_t)row * a.cap + i];
+            key = ((unsigned long long)(uint32_t)id << 32) | __float_as_uint(q);
+            if (id == d)
+                s_pd = __fdiv_rn(q, total_p);
+        }
+        kp[i] = key;
+    }
+    for (uint32_t i = tid; i < n2q; i += kPqThreads) {
+        unsigned long long key = ~0ull;
+        if (i < nq) {
+            const int32_t id = a.q_ids[(size_t)row * a.cap + i];
+            key = ((unsigned long long)(uint32_t)id << 32) | __float_as_uint(a.q_q[(size_t)row * a.cap + i]);
+        }
+        kq[i] = key;
+    }
+    __syncthreads();
+    const float pd = s_pd;
+    const float qd = a.q_prob[row];
+    const bool acc = __fmul_rn(a.u_accept[row], qd) < pd;
+    if (acc) {
+        if (tid == 0) {
+            a.accepted[row] = 1;
+            a.token[row] = d;
+            if (a.flags) a.flags[row] = fl;
+        }
+        return;
+    }
+    // sort both lists by id
+    for (uint32_t k = 2; k <= max(n2p, n2q); k <<= 1) {
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            for (uint32_t i = tid; i < max(n2p, n2q); i += kPqThreads) {
+                const uint32_t o = i ^ j;
+                if (o > i) {
+                    const bool up = (i & k) == 0;
+                    if (k <= n2p && i < n2p) {
+                        const unsigned long long x = kp[i], y = kp[o];
+                        if ((x > y) == up) { kp[i] = y; kp[o] = x; }
+                    }
+                    if (k <= n2q && i < n2q) {
+                        const unsigned long long x = kq[i], y = kq[o];
+                        if ((x > y) == up) { kq[i] = y; kq[o] = x; }
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0) {
+        // two sequential merges: the float total of the residual, then the walk
+        float total_r = 0.0f;
+        uint32_t n_res = 0;
+        for (int pass = 0; pass < 2; ++pass) {
+            float r = __fmul_rn(a.u_resample[row], total_r);
+            int32_t tok = d, last = d;
+            bool done = false;
+            uint32_t i = 0, j = 0;
+            while ((i < np || j < nq) && !done) {
+                const uint32_t ip = i < np ? (uint32_t)(kp[i] >> 32) : 0xffffffffu;
+                const uint32_t iq = j < nq ? (uint32_t)(kq[j] >> 32) : 0xffffffffu;
+                float pn = 0.0f, qn = 0.0f;
+                uint32_t id;
+                if (ip < iq) {
+                    id = ip;
+                    pn = __fdiv_rn(__uint_as_float((uint32_t)(kp[i] & 0xffffffffull)), total_p);
+                    ++i;
+                } else if (iq < ip) {
+                    id = iq;
+                    qn = __fdiv_rn(__uint_as_float((uint32_t)(kq[j] & 0xffffffffull)), total_q);
+                    ++j;
+                } else {
+                    id = ip;
+                    pn = __fdiv_rn(__uint_as_float((uint32_t)(kp[i] & 0xffffffffull)), total_p);
+                    qn = __fdiv_rn(__uint_as_float((uint32_t)(kq[j] & 0xffffffffull)), total_q);
+                    ++i;
+                    ++j;
+                }
+                const float res = __fsub_rn(pn, qn);
+                if (res > 0.0f) {
+                    if (pass == 0) {
+                        total_r = __fadd_rn(total_r, res);
+                        ++n_res;
+                    } else {
+                        last = (int32_t)id;
+                        if (r < res) {
+                            tok = (int32_t)id;
+                            done = true;
+                        } else {
+                            r = __fsub_rn(r, res);
+                        }
+                    }
+                }
+            }
+            if (pass == 1) {
+                if (!done)
+                    tok = last;
+                a.accepted[row] = 0;
+                a.token[row] = n_res ? tok : d;
+                if (a.flags) a.flags[row] = fl;
+            }
+        }
+    }
+}
+
+cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream)
+{
+    if (a.batch == 0)
+        return cudaSuccess;
+    uint32_t cap2 = 2;
+    while (cap2 < a.cap)
+        cap2 <<= 1;
+    const size_t smem = 2 * (size_t)cap2 * 8;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(pq_resolve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess)
+            return e;
+        configured = true;
+    }
+    pq_resolve_kernel<<<a.batch, kPqThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+// ---- acceptance loop of a speculative round (src/gen/session.cpp:481-496, 505) -------------------------------------
+__global__ void spec_resolve_kernel(uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
+                                    int32_t* n_kept, int32_t* next_token)
+{
+    const uint32_t sq = blockIdx.x * blockDim.x + threadIdx.x;
+    if (sq >= n_seq)
+        return;
+    uint32_t kept = 0;
+    while (kept + 1 < n_pos && accepted[(size_t)sq * n_pos + kept])
+        ++kept;
+    n_kept[sq] = (int32_t)kept;
+    next_token[sq] = token[(size_t)sq * n_pos + kept]; // the replacement, or the bonus position's token
+}
+
+cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
+                                int32_t* n_kept, int32_t* next_token, cudaStream_t stream)
+{
+    if (n_seq == 0)
+        return cudaSuccess;
+    spec_resolve_kernel<<<(n_seq + 127) / 128, 128, 0, stream>>>(n_seq, n_pos, accepted, token, n_kept, next_token);
+    return cudaGetLastError();
+}
+
+} // namespace mk

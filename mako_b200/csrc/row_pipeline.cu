@@ -1,0 +1,881 @@
+// The fused row pipeline of the token sampler for sm_100a: one CTA per row, one pass over the row in HBM.
+//
+// What it replaces: mako::gen::Sampler::distribution / draw / sample / verify (src/gen/sampler.cpp:20-107), which
+// the reference runs on the host, one row at a time, over a copy of the logits.
+//
+// Shape of the kernel (352 threads = 11 warps, ~92 KB shared memory, two CTAs per SM):
+//   warp 0        producer: streams the row through a 4-stage ring of 16 KB tiles with untiled bulk asynchronous
+//                 copies (TMA, cp.async.bulk, no multicast), completion on an mbarrier per stage.
+//   warps 1-2     fix-up: once a tile has landed, apply the sparse edits in shared memory — logit bias, then the
+//                 repetition / presence / frequency penalties of the token history, each distinct id once with its
+//                 count (sampler.cpp:23-28). The history is bucketed by tile in shared memory at kernel start;
+//                 counts come from a 16-bit histogram of the tile's ids.
+//   warps 3-10    readers: 128-bit shared loads, allowed-token mask, running row maximum (warp shuffles), and
+//                 collection of every element that can still become a candidate: the keep thresholds of min_p,
+//                 top_k and top_p are all lower-bounded by a function of the running maximum (or of a histogram of
+//                 order-preserving float keys for top_k) that only rises while the row streams, so filtering with
+//                 the current bound keeps a superset of the final candidates.
+//   all warps     finish: exact weights q = expf((l - max) * inv_t) for the few collected elements with the host
+//                 library's float exponential (device_expf.cuh), min_p, top_k, top_p, and the sequential float
+//                 walk of the draw — in the reference's precision and order, because token ids depend on both.
+//
+// Numeric contract (what makes ids bit-exact): IEEE division and no FMA contraction in the penalties and in
+// (l - max) * inv_t; q through expf_host_exact; top_p sums in double; total and the walk in float, left to right.
+#include "row_pipeline.h"
+
+#include "device_expf.cuh"
+#include "ptx.cuh"
+
+#include <cfloat>
+
+namespace mk {
+
+namespace {
+
+constexpr int kTile = 4096;   // floats per tile
+constexpr int kStages = 4;
+constexpr int kProducerThreads = 32;
+constexpr int kFixers = 64;
+constexpr int kReaders = 256;
+constexpr int kThreads = kProducerThreads + kFixers + kReaders;
+constexpr int kReaderWarps = kReaders / 32;
+constexpr int kHistCap = 4096;  // history entries bucketed in shared memory; longer histories scan global memory
+constexpr int kMaxTiles = 1024; // n_vocab <= 4 Mi columns
+constexpr int kSortCap = kStages * kTile * 4 / 8; // 8192 64-bit sort keys fit in the ring
+constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
+constexpr int kBinShift = 21;
+constexpr uint32_t kBarFix = 1, kBarRead = 2;
+
+struct __align__(128) Smem {
+    float ring[kStages][kTile];
+    uint32_t cnt[kTile / 2];        // per-tile id counts, two 16-bit counters per word
+    uint16_t hs[kHistCap];          // history as column-within-tile, bucketed by tile
+    uint32_t hstart[kMaxTiles + 1]; // bucket boundaries
+    uint32_t hist[kBins];           // top_k: counts per key bin
+    double warp_sum[kReaderWarps];
+    uint64_t full[kStages], ready[kStages], empty[kStages];
+    unsigned long long best_key;    // (order key of the row maximum << 32) | ~column: first argmax wins
+    uint32_t m_key;                 // running maximum, as order key
+    uint32_t thr_topk_bits;         // top_k lower bound (float bits)
+    uint32_t ncand;                 // raw candidates appended
+    uint32_t nsurv;                 // candidates surviving the exact filter
+    uint32_t abort_flag;
+    uint32_t nan0;                  // column 0 (token id 0) is NaN: the reference's max_element keeps it
+    uint32_t hi_group;              // highest non-empty group of 32 histogram bins
+    uint32_t n_final;
+    uint32_t flags;
+};
+
+struct RowCfg {
+    float temperature, inv_t, minp_eff, top_p;
+    uint32_t top_k;
+    float rep, presence, frequency;
+    bool greedy, hist_mode, need_sum, use_topp, pen_active;
+    float delta_w;      // keep elements with l >= running max - delta_w
+    bool force_none;    // inv_t is inf/NaN: no finite weight can exist
+};
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ RowCfg make_cfg(const mk_sampling_params& p, uint32_t n_vocab, int mode, uint32_t vp_k)
+{
+    RowCfg c;
+    c.temperature = p.temperature;
+    c.greedy = p.temperature <= 0.0f;                       // sampler.hpp:26
+    c.inv_t = __fdiv_rn(1.0f, p.temperature);               // sampler.cpp:29
+    c.minp_eff = (1.0f < p.min_p) ? 1.0f : p.min_p;         // std::min(min_p, 1.0f), sampler.cpp:34
+    c.top_p = p.top_p;
+    c.top_k = p.top_k;
+    c.rep = p.repetition_penalty;
+    c.presence = p.presence_penalty;
+    c.frequency = p.frequency_penalty;
+    c.pen_active = !(c.rep == 1.0f && c.presence == 0.0f && c.frequency == 0.0f);
+    c.use_topp = p.top_p < 1.0f;
+    c.hist_mode = !c.greedy && p.top_k > 0 && p.top_k < n_vocab;
+    const bool minp_on = c.minp_eff > 0.0f;
+    // The float total over "all candidates" is only needed when top_p is the only truncation.
+    c.need_sum = !c.greedy && c.use_topp && !minp_on && !c.hist_mode;
+    c.force_none = !(c.inv_t < __int_as_float(0x7f800000)) || !(c.inv_t == c.inv_t);
+    if (mode == kModeVpLocal) {
+        c.hist_mode = vp_k < n_vocab;
+        c.top_k = vp_k;
+        c.need_sum = true;
+        c.use_topp = false;
+        c.minp_eff = 0.0f;
+    }
+    // Distance below the row maximum, in units of (l - max) * inv_t, past which an element cannot be kept:
+    //   q == 0 below about -103.98 (float underflow of expf);
+    //   q < min_p below ln(min_p);
+    //   with top_p alone, an element with q < (1 - top_p) / n_vocab is outside the nucleus, because all such
+    //   elements together weigh less than (1 - top_p) * total (total >= 1: the maximum itself has q = 1).
+    float d = 104.2f;
+    if (mode != kModeVpLocal) {
+        if (minp_on)
+            d = fminf(d, -logf(c.minp_eff));
+        if (c.need_sum) {
+            float a = (1.0f - c.top_p) / (float)n_vocab;
+            a = fminf(a, 1.0f);
+            if (a > 0.0f)
+                d = fminf(d, -logf(a));
+        }
+    }
+    d = d * 1.001f + 1e-3f;
+    c.delta_w = d * fmaxf(c.temperature, 0.0f);
+    if (!(c.delta_w == c.delta_w))
+        c.delta_w = __int_as_float(0x7f800000);
+    return c;
+}
+
+// Threshold on the (edited) logit for the current running maximum; never -inf, so masked elements never pass.
+__device__ __forceinline__ float keep_threshold(const RowCfg& c, float m_run)
+{
+    if (c.force_none || !(m_run < __int_as_float(0x7f800000)))
+        return __int_as_float(0x7f800000); // no finite weight can exist (an infinite maximum makes l - max NaN or -inf)
+    const float t = m_run - c.delta_w - fabsf(m_run) * 1e-6f;
+    return fmaxf(t, -FLT_MAX);
+}
+
+// Penalties of one generated token with count n, exactly as sampler.cpp:24-27.
+__device__ __forceinline__ float penalise(float l, uint32_t n, const RowCfg& c)
+{
+    if (c.rep != 1.0f)
+        l = (l > 0.0f) ? __fdiv_rn(l, c.rep) : __fmul_rn(l, c.rep);
+    const float step = __fadd_rn(c.presence, __fmul_rn(c.frequency, (float)n));
+    return __fsub_rn(l, step);
+}
+
+__device__ __forceinline__ unsigned long long pack_by_weight(float q, uint32_t col)
+{
+    // ascending key order = (q descending, column ascending); q > 0 so its bit pattern is monotone
+    return ((unsigned long long)(~__float_as_uint(q)) << 32) | col;
+}
+__device__ __forceinline__ unsigned long long pack_by_column(float q, uint32_t col)
+{
+    return ((unsigned long long)col << 32) | __float_as_uint(q);
+}
+
+// Bitonic sort of n2 (power of two) 64-bit keys in shared memory by the whole CTA.
+__device__ void block_sort(unsigned long long* keys, uint32_t n2)
+{
+    for (uint32_t k = 2; k <= n2; k <<= 1) {
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            for (uint32_t i = threadIdx.x; i < n2; i += kThreads) {
+                const uint32_t l = i ^ j;
+                if (l > i) {
+                    const unsigned long long a = keys[i], b = keys[l];
+                    const bool up = (i & k) == 0;
+                    if ((a > b) == up) {
+                        keys[i] = b;
+                        keys[l] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+} // namespace
+
+__global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKernelArgs a)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Smem& s = *reinterpret_cast<Smem*>(smem_raw);
+
+    const uint32_t row = blockIdx.x;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5, lane = tid & 31;
+    const uint32_t V = a.n_vocab;
+    const uint32_t n_tiles = (V + kTile - 1) / kTile;
+    const float* __restrict__ lrow = a.logits + (size_t)row * a.ld;
+    const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
+    const RowCfg cfg = make_cfg(prm, V, a.mode, a.vp_k);
+
+    const uint32_t hlen_all = a.history ? (a.history_len ? (uint32_t)max(a.history_len[row], 0) : a.n_history) : 0u;
+    const bool has_hist = !cfg.greedy && cfg.pen_active && hlen_all > 0;
+    const uint32_t hlen = has_hist ? hlen_all : 0u;
+    const int32_t* __restrict__ hrow = a.history ? a.history + (size_t)row * a.history_ld : nullptr;
+    const bool long_history = hlen > (uint32_t)kHistCap;
+    const uint32_t nb = a.bias ? a.n_bias : 0u;
+    const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
+    const bool has_fix = has_hist || nb > 0;
+    const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
+    uint2* __restrict__ scratch = a.scratch + (size_t)row * a.scratch_cap;
+
+    // ---- set-up -------------------------------------------------------------------------------------------------
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.ready[i], kFixers / 32);
+            mbar_init(&s.empty[i], kReaderWarps);
+        }
+        s.best_key = 0ull;
+        s.m_key = order_key(-__int_as_float(0x7f800000));
+        s.thr_topk_bits = __float_as_uint(-FLT_MAX);
+        s.ncand = 0;
+        s.nsurv = 0;
+        s.abort_flag = 0;
+        s.nan0 = 0;
+        s.hi_group = 0;
+        s.n_final = 0;
+        s.flags = 0;
+        fence_barrier_init();
+    }
+    for (uint32_t i = tid; i < kTile / 2; i += kThreads)
+        s.cnt[i] = 0;
+    if (cfg.hist_mode)
+        for (uint32_t i = tid; i < kBins; i += kThreads)
+            s.hist[i] = 0;
+    if (has_hist && !long_history)
+        for (uint32_t i = tid; i <= n_tiles; i += kThreads)
+            s.hstart[i] = 0;
+    __syncthreads();
+
+    if (has_hist && !long_history) {
+        // Bucket the history by tile: count, exclusive scan, scatter (counting sort on column / kTile).
+        for (uint32_t j = tid; j < hlen; j += kThreads) {
+            const int64_t col = (int64_t)hrow[j] - a.id_offset;
+            if (col >= 0 && col < (int64_t)V)
+                atomicAdd(&s.hstart[(uint32_t)col / kTile + 1], 1u);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t carry = 0;
+            for (uint32_t base = 0; base <= n_tiles; base += 32) {
+                const uint32_t i = base + lane;
+                uint32_t v = (i <= n_tiles) ? s.hstart[i] : 0u;
+                uint32_t x = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+                    if ((int)lane >= o)
+                        x += y;
+                }
+                if (i <= n_tiles)
+                    s.hstart[i] = carry + x; // inclusive: hstart[t+1] = entries in tiles 0..t
+                carry += __shfl_sync(0xffffffffu, x, 31);
+            }
+        }
+        __syncthreads();
+        // hstart[t] now holds the END of bucket t-1 = START of bucket t (hstart[0] = 0). Scatter with the
+        // tile's own 16-bit counters as cursors (they are free until the streaming starts), then clear them.
+        for (uint32_t j = tid; j < hlen; j += kThreads) {
+            const int64_t col = (int64_t)hrow[j] - a.id_offset;
+            if (col >= 0 && col < (int64_t)V) {
+                const uint32_t t = (uint32_t)col / kTile;
+                const uint32_t pos = s.hstart[t] + atomicAdd(&s.cnt[t], 1u);
+                s.hs[pos] = (uint16_t)((uint32_t)col % kTile);
+            }
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < n_tiles; i += kThreads)
+            s.cnt[i] = 0;
+        __syncthreads();
+    }
+
+    // ---- streaming ----------------------------------------------------------------------------------------------
+    float best = -__int_as_float(0x7f800000);
+    int32_t best_col = -1;
+    double sum_acc = 0.0; // sum of exp2((l - best) * c2) over this thread's elements (need_sum)
+
+    if (warp == 0) {
+        // producer
+        for (uint32_t t = 0; t < n_tiles; ++t) {
+            const uint32_t st = t % kStages, k = t / kStages;
+            float* dst = s.ring[st];
+            const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
+            const float* src = lrow + (size_t)t * kTile;
+            if (k > 0) {
+                bool ok = true;
+                if (lane == 0)
+                    ok = mbar_wait(&s.empty[st], (k - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0)
+                        atomicExch(&s.abort_flag, 1u);
+                    break;
+                }
+            }
+            if (*(volatile uint32_t*)&s.abort_flag)
+                break;
+            if (a.use_bulk_copy) {
+                if (lane == 0) {
+                    fence_proxy_async();
+                    const uint32_t bytes = (n_t * 4u) & ~15u;
+                    for (uint32_t e = bytes / 4; e < n_t; ++e)
+                        dst[e] = src[e];
+                    if (bytes > 0) {
+                        mbar_arrive_expect_tx(&s.full[st], bytes);
+                        bulk_load(dst, src, bytes, &s.full[st]);
+                    } else {
+                        mbar_arrive(&s.full[st]);
+                    }
+                }
+            } else {
+                for (uint32_t e = lane; e < n_t; e += 32)
+                    dst[e] = src[e];
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&s.full[st]);
+            }
+        }
+    } else if (warp <= kFixers / 32) {
+        // fix-up
+        if (has_fix) {
+            const uint32_t ft = tid - kProducerThreads;
+            for (uint32_t t = 0; t < n_tiles; ++t) {
+                const uint32_t st = t % kStages, k = t / kStages;
+                float* tp = s.ring[st];
+                const uint32_t base = t * kTile;
+                const uint32_t n_t = min((uint32_t)kTile, V - base);
+                // After a timeout the remaining tiles are walked without waiting, so that the named barriers below
+                // stay matched across the fix-up threads.
+                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 22)))
+                    atomicExch(&s.abort_flag, 1u);
+                if (nb > 0) {
+                    for (uint32_t j = ft; j < nb; j += kFixers) {
+                        const mk_bias be = brow[j];
+                        const int64_t loc = (int64_t)be.id - a.id_offset - (int64_t)base;
+                        if (be.id >= 0 && loc >= 0 && loc < (int64_t)n_t)
+                            tp[loc] = __fadd_rn(tp[loc], be.value);
+                    }
+                    if (has_hist)
+                        named_barrier(kBarFix, kFixers);
+                }
+                if (has_hist) {
+                    if (!long_history) {
+                        const uint32_t e0 = s.hstart[t], e1 = s.hstart[t + 1];
+                        if (e1 > e0) {
+                            for (uint32_t e = e0 + ft; e < e1; e += kFixers) {
+                                const uint32_t loc = s.hs[e];
+                                atomicAdd(&s.cnt[loc >> 1], 1u << ((loc & 1u) * 16u));
+                            }
+                            named_barrier(kBarFix, kFixers);
+                            for (uint32_t e = e0 + ft; e < e1; e += kFixers) {
+                                const uint32_t loc = s.hs[e];
+                                const uint32_t sh = (loc & 1u) * 16u;
+                                // Claim: the first thread to clear the counter owns the id and its count.
+                                const uint32_t old = atomicAnd(&s.cnt[loc >> 1], ~(0xffffu << sh));
+                                const uint32_t n = (old >> sh) & 0xffffu;
+                                if (n)
+                                    tp[loc] = penalise(tp[loc], n, cfg);
+                            }
+                        }
+                    } else {
+                        for (uint32_t j = ft; j < hlen; j += kFixers) {
+                            const int64_t loc = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
+                            if (loc >= 0 && loc < (int64_t)n_t)
+                                atomicAdd(&s.cnt[(uint32_t)loc >> 1], 1u << (((uint32_t)loc & 1u) * 16u));
+                        }
+                        named_barrier(kBarFix, kFixers);
+                        for (uint32_t j = ft; j < hlen; j += kFixers) {
+                            const int64_t loc64 = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
+                            if (loc64 >= 0 && loc64 < (int64_t)n_t) {
+                                const uint32_t loc = (uint32_t)loc64, sh = (loc & 1u) * 16u;
+                                const uint32_t old = atomicAnd(&s.cnt[loc >> 1], ~(0xffffu << sh));
+                                const uint32_t n = (old >> sh) & 0xffffu;
+                                if (n)
+                                    tp[loc] = penalise(tp[loc], n, cfg);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&s.ready[st]);
+            }
+        }
+    } else {
+        // readers
+        const uint32_t rt = tid - kProducerThreads - kFixers;
+        const uint32_t rwarp = rt >> 5;
+        uint64_t* const avail = has_fix ? s.ready : s.full;
+        const float c2 = cfg.inv_t * 1.4426950408889634f;
+        const float ninf = -__int_as_float(0x7f800000);
+        const bool collect = !cfg.greedy;
+        float warp_pub = ninf;
+        for (uint32_t t = 0; t < n_tiles; ++t) {
+            const uint32_t st = t % kStages, k = t / kStages;
+            const uint32_t base = t * kTile;
+            uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+            if (mrow) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t i0 = base + j * 1024 + rt * 4;
+                    mw[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
+                }
+            }
+            if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 22)))
+                atomicExch(&s.abort_flag, 1u); // keep walking: the named barriers below must stay matched
+            float w[16];
+            const float4* tp4 = reinterpret_cast<const float4*>(s.ring[st]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 v = tp4[j * 256 + rt];
+                w[4 * j + 0] = v.x;
+                w[4 * j + 1] = v.y;
+                w[4 * j + 2] = v.z;
+                w[4 * j + 3] = v.w;
+            }
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&s.empty[st]);
+
+            if (mrow) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t bits = mw[j] >> ((rt * 4) & 31);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (!((bits >> c) & 1u))
+                            w[4 * j + c] = ninf;
+                }
+            }
+            if (base + kTile > V) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (base + j * 1024 + rt * 4 + c >= V)
+                            w[4 * j + c] = ninf;
+            }
+            if (t == 0 && rt == 0 && w[0] != w[0])
+                s.nan0 = 1;
+
+            float tm = ninf;
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+                tm = fmaxf(tm, w[e]);
+            const float old_best = best;
+            if (tm > best) {
+                best = tm;
+#pragma unroll
+                for (int e = 15; e >= 0; --e)
+                    if (w[e] == tm)
+                        best_col = (int32_t)(base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+            }
+            if (__any_sync(0xffffffffu, tm > warp_pub)) {
+                const float wm = warp_max(tm);
+                if (wm > warp_pub) {
+                    warp_pub = wm;
+                    if (lane == 0)
+                        atomicMax(&s.m_key, order_key(wm));
+                }
+            }
+            if (cfg.need_sum && best > ninf) {
+                if (best > old_best)
+                    sum_acc *= (double)exp2f((old_best - best) * c2);
+                float p = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    p += exp2f((w[e] - best) * c2);
+                sum_acc += (double)p;
+            }
+
+            float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
+            if (cfg.hist_mode) {
+                // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
+                // where the count from the top reaches k bounds the k-th largest from below.
+                thr = fmaxf(thr, __uint_as_float(*(volatile uint32_t*)&s.thr_topk_bits));
+                if (tm >= thr) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        if (w[e] >= thr) {
+                            const uint32_t bin = order_key(w[e]) >> kBinShift;
+                            atomicAdd(&s.hist[bin], 1u);
+                            atomicMax(&s.hi_group, bin >> 5);
+                        }
+                }
+                named_barrier(kBarRead, kReaders);
+                if (rwarp == 0) {
+                    uint32_t cum = 0;
+                    int found = -1;
+                    for (int g = (int)*(volatile uint32_t*)&s.hi_group; g >= 0 && found < 0; --g) {
+                        const uint32_t cbin = s.hist[g * 32 + lane];
+                        uint32_t suf = cbin; // suffix sum over lanes >= lane
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const uint32_t y = __shfl_down_sync(0xffffffffu, suf, o);
+                            if ((int)lane + o < 32)
+                                suf += y;
+                        }
+                        const uint32_t hit = __ballot_sync(0xffffffffu, cum + suf >= cfg.top_k);
+                        if (hit)
+                            found = g * 32 + (31 - __clz(hit));
+                        cum += __shfl_sync(0xffffffffu, suf, 0);
+                    }
+                    if (lane == 0 && found >= 0) {
+                        const float edge = key_to_float((uint32_t)found << kBinShift);
+                        // the lowest key of a bin is its smallest float; NaN keys (bin 0) never get here
+                        if (edge == edge)
+                            s.thr_topk_bits = __float_as_uint(fmaxf(edge, -FLT_MAX));
+                    }
+                }
+                named_barrier(kBarRead, kReaders);
+                thr = fmaxf(thr, __uint_as_float(*(volatile uint32_t*)&s.thr_topk_bits));
+            }
+            if (collect && tm >= thr) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    if (w[e] >= thr) {
+                        const uint32_t slot = atomicAdd(&s.ncand, 1u);
+                        if (slot < a.scratch_cap)
+                            scratch[slot] =
+                                make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                    }
+            }
+        }
+        if (best_col >= 0)
+            atomicMax(&s.best_key,
+                      ((unsigned long long)order_key(best) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)best_col));
+    }
+    __syncthreads();
+
+    // ---- finish -------------------------------------------------------------------------------------------------
+    if (s.abort_flag) {
+        // A bounded wait ran out. Give copies still in flight time to land before the CTA's shared memory is
+        // released, then report.
+        for (int i = 0; i < 64; ++i)
+            __nanosleep(1000);
+        if (tid == 0) {
+            if (a.token) a.token[row] = -1;
+            if (a.flags) a.flags[row] = MK_FLAG_TIMEOUT;
+            if (a.n_cand) a.n_cand[row] = 0;
+            if (a.accepted) a.accepted[row] = 0;
+        }
+        return;
+    }
+
+    const bool any_finite = s.best_key != 0ull;
+    float m = any_finite ? key_to_float((uint32_t)(s.best_key >> 32)) : -__int_as_float(0x7f800000);
+    uint32_t arg_col = any_finite ? (0xffffffffu - (uint32_t)(s.best_key & 0xffffffffull)) : 0u;
+    if (s.nan0) { // max_element keeps a NaN in front: every weight is NaN, the first column is returned
+        m = __int_as_float(0x7fc00000);
+        arg_col = 0;
+    }
+    uint32_t flags = 0;
+    if (mrow && !any_finite && !s.nan0)
+        flags |= MK_FLAG_ALL_MASKED;
+
+    // exact row total for need_sum: sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
+    double total_approx = 0.0;
+    if (cfg.need_sum) {
+        double part = 0.0;
+        if (warp > kFixers / 32) {
+            const float c2 = cfg.inv_t * 1.4426950408889634f;
+            if (best > -__int_as_float(0x7f800000) && sum_acc > 0.0)
+                part = sum_acc * exp2((double)(best - m) * (double)c2);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0)
+                s.warp_sum[warp - 1 - kFixers / 32] = part;
+        }
+        __syncthreads();
+        for (int i = 0; i < kReaderWarps; ++i)
+            total_approx += s.warp_sum[i];
+    }
+
+    if (a.mode == kModeVpLocal) {
+        // Shard record: header {max, n, sum} then the k best (logit, global id), by (logit desc, id asc).
+        unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
+        const uint32_t n_raw = min(s.ncand, min(a.scratch_cap, (uint32_t)kSortCap));
+        const bool over = s.ncand > min(a.scratch_cap, (uint32_t)kSortCap);
+        uint32_t n2 = 2;
+        while (n2 < n_raw)
+            n2 <<= 1;
+        for (uint32_t i = tid; i < n2; i += kThreads) {
+            unsigned long long key = ~0ull;
+            if (i < n_raw) {
+                const uint2 c = scratch[i];
+                key = ((unsigned long long)(~order_key(__uint_as_float(c.x))) << 32) | c.y;
+            }
+            keys[i] = key;
+        }
+        __syncthreads();
+        block_sort(keys, n2);
+        unsigned char* rec = reinterpret_cast<unsigned char*>(a.vp_records) + (size_t)row * vp_record_bytes(a.vp_k);
+        const uint32_t n_out = min(n_raw, a.vp_k);
+        if (tid == 0) {
+            float* hf = reinterpret_cast<float*>(rec);
+            uint32_t* hu = reinterpret_cast<uint32_t*>(rec);
+            hf[0] = m;
+            hu[1] = n_out | (over ? 0x80000000u : 0u) | ((V > a.vp_k) ? 0x40000000u : 0u);
+            *reinterpret_cast<double*>(rec + 8) = total_approx;
+        }
+        for (uint32_t i = tid; i < a.vp_k; i += kThreads) {
+            uint2 o = make_uint2(__float_as_uint(-__int_as_float(0x7f800000)), 0xffffffffu);
+            if (i < n_out) {
+                const unsigned long long key = keys[i];
+                const uint32_t ok = ~(uint32_t)(key >> 32);
+                o.x = __float_as_uint(key_to_float(ok));
+                o.y = (uint32_t)((int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset);
+            }
+            reinterpret_cast<uint2*>(rec + kVpHeaderBytes)[i] = o;
+        }
+        return;
+    }
+
+    if (cfg.greedy) {
+        // sampler.cpp:77-78, 88-91: first maximum of the row as handed over (bias and mask applied, no penalties)
+        if (tid == 0) {
+            const int32_t t = (int32_t)arg_col + a.id_offset;
+            if (a.token) a.token[row] = t;
+            if (a.prob) a.prob[row] = 1.0f;
+            if (a.n_cand) a.n_cand[row] = 1;
+            if (a.flags) a.flags[row] = flags;
+            if (a.cand_ids && a.cand_cap) a.cand_ids[(size_t)row * a.cand_cap] = t;
+            if (a.cand_q && a.cand_cap) a.cand_q[(size_t)row * a.cand_cap] = 1.0f;
+            if (a.total_out) a.total_out[row] = 1.0f;
+            if (a.mode == kModeVerify && a.accepted)
+                a.accepted[row] = (a.draft[row] == t) ? 1 : 0;
+        }
+        return;
+    }
+
+    // exact weights of the collected elements, min_p filter (sampler.cpp:33-35)
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
+    const uint32_t n_raw = min(s.ncand, a.scratch_cap);
+    bool overflow = s.ncand > a.scratch_cap;
+    if (!s.nan0) {
+        // Elements collected while the running maximum was still low are dropped by the final bound first.
+        const float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        for (uint32_t i = tid; i < n_raw; i += kThreads) {
+            const uint2 c = scratch[i];
+            if (!(__uint_as_float(c.x) >= thr_final))
+                continue;
+            const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
+            const float q = expf_host_exact(x);
+            if (q >= cfg.minp_eff && q > 0.0f) {
+                const uint32_t slot = atomicAdd(&s.nsurv, 1u);
+                if (slot < (uint32_t)kSortCap)
+                    keys[slot] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
+            }
+        }
+    }
+    __syncthreads();
+    uint32_t n = s.nsurv;
+    if (n > (uint32_t)kSortCap)
+        overflow = true;
+    if (overflow) {
+        if (tid == 0) {
+            if (a.token) a.token[row] = -1;
+            if (a.prob) a.prob[row] = 0.0f;
+            if (a.flags) a.flags[row] = flags | MK_FLAG_OVERFLOW;
+            if (a.n_cand) a.n_cand[row] = s.ncand;
+            if (a.accepted) a.accepted[row] = 0;
+            if (a.total_out) a.total_out[row] = 0.0f;
+        }
+        return;
+    }
+    if (n == 0) { // sampler.cpp:37-38
+        flags |= MK_FLAG_NO_CANDIDATE;
+        if (tid == 0)
+            keys[0] = ((unsigned long long)__float_as_uint(1.0f) << 32) | arg_col;
+        n = 1;
+        __syncthreads();
+    }
+    const bool cut_k = cfg.top_k > 0 && cfg.top_k < n;       // sampler.cpp:39
+    const bool sorted = cut_k || cfg.use_topp;               // else ascending id
+    uint32_t n2 = 2;
+    while (n2 < n)
+        n2 <<= 1;
+    for (uint32_t i = tid; i < n2; i += kThreads) {
+        unsigned long long key = ~0ull;
+        if (i < n) {
+            const unsigned long long raw = keys[i];
+            const float q = __uint_as_float((uint32_t)(raw >> 32));
+            const uint32_t col = (uint32_t)(raw & 0xffffffffull);
+            key = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
+        }
+        keys[i] = key;
+    }
+    __syncthreads();
+    if (n > 1)
+        block_sort(keys, n2);
+
+    if (tid == 0) {
+        auto q_at = [&](uint32_t i) -> float {
+            const unsigned long long key = keys[i];
+            return sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
+        };
+        auto col_at = [&](uint32_t i) -> uint32_t {
+            const unsigned long long key = keys[i];
+            return sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
+        };
+        if (cut_k) {
+            // sampler.cpp:40-42. Ties in q with the k-th weight are ordered by id among ALL elements with that
+            // weight; elements below the histogram bound were not collected, so the bound itself must map to a
+            // strictly smaller weight than the k-th.
+            const float qk = q_at(cfg.top_k - 1);
+            const float edge = __uint_as_float(s.thr_topk_bits);
+            if (edge > -FLT_MAX) {
+                const float qe = expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t));
+                if (qe >= qk)
+                    flags |= MK_FLAG_GUARD_BAND;
+            }
+            n = cfg.top_k;
+        }
+        if (cfg.use_topp) { // sampler.cpp:44-61
+            double total = 0.0;
+            double band;
+            if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
+                total = total_approx;
+                band = 1e-5 * total;
+            } else {
+                for (uint32_t i = 0; i < n; ++i)
+                    total += (double)q_at(i);
+                band = 0x1p-40 * total;
+            }
+            const double want = (double)cfg.top_p * total;
+            double run = 0.0, prev = 0.0;
+            uint32_t k = 0;
+            while (k < n && run < want) {
+                prev = run;
+                run += (double)q_at(k++);
+            }
+            if (cfg.need_sum && run < want)
+                flags |= MK_FLAG_GUARD_BAND; // the collected list ended before the nucleus did
+            if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
+                flags |= MK_FLAG_GUARD_BAND;
+            n = max(k, 1u);
+        }
+        // total and the walk, float, left to right (sampler.cpp:64-73, 80-83)
+        float total = 0.0f;
+        float q_draft = 0.0f;
+        int32_t draft = (a.mode == kModeVerify) ? a.draft[row] : -1;
+        for (uint32_t i = 0; i < n; ++i) {
+            const float q = q_at(i);
+            total = __fadd_rn(total, q);
+            if (a.mode == kModeVerify && (int32_t)col_at(i) + a.id_offset == draft)
+                q_draft = q;
+        }
+        int32_t tok = -1;
+        float prob = 0.0f;
+        int32_t acc = 0;
+        if (a.mode == kModeDistOnly) {
+            tok = (int32_t)col_at(0) + a.id_offset;
+            prob = __fdiv_rn(q_at(0), total);
+        } else {
+            float r;
+            bool skip_draft = false;
+            float walk_total = total;
+            if (a.mode == kModeVerify) { // sampler.cpp:100-106
+                acc = __fmul_rn(a.u[row], total) < q_draft;
+                if (acc) {
+                    tok = draft;
+                    prob = __fdiv_rn(q_draft, total);
+                } else {
+                    skip_draft = true;
+                    walk_total = __fsub_rn(total, q_draft);
+                    const bool only_draft = (n == 1 && (int32_t)col_at(0) + a.id_offset == draft);
+                    if (only_draft) {
+                        tok = draft;
+                        prob = 1.0f;
+                    }
+                }
+            }
+            if (tok < 0) {
+                const float uu = (a.mode == kModeVerify) ? a.u2[row] : a.u[row];
+                r = __fmul_rn(uu, walk_total);
+                const float eps = 1e-6f * walk_total;
+                int32_t last = -1;
+                float last_q = 0.0f;
+                bool first = true, done = false;
+                for (uint32_t i = 0; i < n && !done; ++i) {
+                    const int32_t id = (int32_t)col_at(i) + a.id_offset;
+                    if (skip_draft && id == draft)
+                        continue;
+                    const float q = q_at(i);
+                    last = id;
+                    last_q = q;
+                    if (r < q) {
+                        tok = id;
+                        prob = __fdiv_rn(q, walk_total);
+                        // boundary below (not for the first candidate) or above (not for the last)
+                        bool more = false;
+                        for (uint32_t j = i + 1; j < n; ++j)
+                            if (!(skip_draft && (int32_t)col_at(j) + a.id_offset == draft))
+                                more = true;
+                        if ((!first && r < eps) || (more && __fsub_rn(q, r) < eps))
+                            flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                        done = true;
+                    } else {
+                        r = __fsub_rn(r, q);
+                        first = false;
+                    }
+                }
+                if (!done) { // rounding: the last candidate (sampler.cpp:72)
+                    tok = last;
+                    prob = __fdiv_rn(last_q, walk_total);
+                }
+            }
+        }
+        if (a.token) a.token[row] = tok;
+        if (a.prob) a.prob[row] = prob;
+        if (a.flags) a.flags[row] = flags;
+        if (a.n_cand) a.n_cand[row] = n;
+        if (a.accepted) a.accepted[row] = acc;
+        if (a.total_out) a.total_out[row] = total;
+        s.n_final = n;
+    }
+    __syncthreads();
+    if (a.cand_ids || a.cand_q) {
+        const uint32_t nf = min(s.n_final, a.cand_cap);
+        for (uint32_t i = tid; i < nf; i += kThreads) {
+            const unsigned long long key = keys[i];
+            const uint32_t col = sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
+            const float q = sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
+            if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)col + a.id_offset;
+            if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + i] = q;
+        }
+    }
+}
+
+size_t row_kernel_smem_bytes()
+{
+    return sizeof(Smem);
+}
+
+cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream_t stream)
+{
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return e;
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(row_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+        if (e != cudaSuccess)
+            return e;
+        configured[dev] = true;
+    }
+    if (batch == 0)
+        return cudaSuccess;
+    row_pipeline_kernel<<<batch, kThreads, sizeof(Smem), stream>>>(a);
+    return cudaGetLastError();
+}
+
+// ---- test hook --------------------------------------------------------------------------------------------------
+__global__ void expf_probe_kernel(const float* x, float* y, uint64_t n)
+{
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n)
+        y[i] = expf_host_exact(x[i]);
+}
+
+cudaError_t launch_expf_probe(const float* x, float* y, uint64_t n, cudaStream_t stream)
+{
+    if (n == 0)
+        return cudaSuccess;
+    expf_probe_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, y, n);
+    return cudaGetLastError();
+}
+
+} // namespace mk

@@ -1,0 +1,98 @@
+// Host-visible declarations of the row pipeline kernels (internal to the library; the public surface is
+// include/mako_b200.h).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/mako_b200.h"
+
+namespace mk {
+
+enum RowMode : int {
+    kModeSample = 0,   // Sampler::sample
+    kModeVerify = 1,   // Sampler::verify with a deterministic draft
+    kModeDistOnly = 2, // candidate list only (target side of p/q verification)
+    kModeVpLocal = 3   // vocab-parallel shard record
+};
+
+struct RowKernelArgs {
+    // inputs
+    const float* logits;
+    uint64_t ld;
+    uint32_t n_vocab;
+    int32_t id_offset;
+    const int32_t* history;
+    uint64_t history_ld;
+    const int32_t* history_len;
+    uint32_t n_history;
+    const uint32_t* mask;
+    uint64_t mask_ld;
+    const mk_bias* bias;
+    uint32_t n_bias;
+    const mk_sampling_params* params_dev;
+    mk_sampling_params params;
+    const float* u;        // sample: draw; verify: acceptance
+    const float* u2;       // verify: redraw
+    const int32_t* draft;  // verify
+    // outputs
+    int32_t* token;
+    float* prob;
+    uint32_t* flags;
+    uint32_t* n_cand;
+    int32_t* cand_ids;
+    float* cand_q;
+    uint32_t cand_cap;
+    int32_t* accepted;     // verify
+    float* total_out;      // optional [batch]: float total of the final list
+    // vocab-parallel
+    void* vp_records;
+    uint32_t vp_k;
+    // scratch owned by the handle
+    uint2* scratch;        // [batch][scratch_cap] raw candidates (logit bits, column)
+    uint32_t scratch_cap;
+    int mode;
+    int use_bulk_copy;     // 1: TMA bulk staging (aligned rows); 0: plain loads
+};
+
+size_t row_kernel_smem_bytes();
+cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream_t stream);
+
+struct VpMergeArgs {
+    const unsigned char* gathered; // [n_shards][batch] records
+    uint32_t n_shards, batch, k, n_vocab_total;
+    const mk_sampling_params* params_dev;
+    mk_sampling_params params;
+    const float* u;
+    int32_t* token;
+    float* prob;
+    uint32_t* flags;
+    uint32_t* n_cand;
+    int32_t* cand_ids;
+    float* cand_q;
+    uint32_t cand_cap;
+};
+cudaError_t launch_vp_merge(const VpMergeArgs& a, cudaStream_t stream);
+
+struct PqResolveArgs {
+    uint32_t batch, cap;
+    const int32_t* p_ids; const float* p_q; const uint32_t* p_n; const uint32_t* p_flags;
+    const int32_t* q_ids; const float* q_q; const uint32_t* q_n; const uint32_t* q_flags;
+    const float* p_total; const float* q_total; // float totals of the two lists (draw order)
+    const float* q_prob;        // probability of the draft token under q
+    const int32_t* draft_token; // drawn from q by the sample launch
+    const float* u_accept; const float* u_resample;
+    int32_t* accepted; int32_t* token; uint32_t* flags;
+};
+cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream);
+
+cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
+                                int32_t* n_kept, int32_t* next_token, cudaStream_t stream);
+
+// Test hook: y[i] = expf_host_exact(x[i]).
+cudaError_t launch_expf_probe(const float* x, float* y, uint64_t n, cudaStream_t stream);
+
+constexpr uint32_t kVpMaxK = 64;
+constexpr uint32_t kVpHeaderBytes = 16;
+__host__ __device__ inline uint32_t vp_record_bytes(uint32_t k) { return kVpHeaderBytes + 8u * k; }
+
+} // namespace mk

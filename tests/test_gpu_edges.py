@@ -1,0 +1,134 @@
+"""GPU edge cases the reference's semantics define: non-finite rows, ties, all-masked rows, per-row parameters,
+long histories, unaligned rows, the host-buffer entry point."""
+import numpy as np
+import pytest
+
+from helpers import Inputs, compare_sample, oracle_sample_rows
+from mako_b200 import synth
+from mako_b200.sampler import SamplingParams, pack_params
+
+pytestmark = pytest.mark.gpu
+
+
+def gpu_rows(factory, logits, params, u, cap=32, **kw):
+    import torch
+    s = factory(logits.shape[1], logits.shape[0], cap)
+    tkw = {}
+    if "history" in kw:
+        tkw["history"] = torch.from_numpy(kw["history"]).cuda()
+    if "mask" in kw:
+        tkw["mask"] = torch.from_numpy(kw["mask"].view(np.int32)).cuda()
+    res = s.sample(torch.from_numpy(logits).cuda(), params, torch.from_numpy(u).cuda(), **tkw)
+    torch.cuda.synchronize()
+    return res
+
+
+def test_nonfinite_rows(gpu_sampler_factory, ref):
+    v = 5000
+    rows = np.zeros((8, v), dtype=np.float32)
+    rng = np.random.default_rng(3)
+    rows[:] = rng.normal(0, 2, size=rows.shape).astype(np.float32)
+    rows[0, :] = -np.inf                      # nothing finite: token 0
+    rows[1, 100] = np.inf                     # an infinite maximum: first +inf
+    rows[1, 4000] = np.inf
+    rows[2, 0] = np.nan                       # NaN in front: max_element keeps it -> token 0
+    rows[3, 17] = np.nan                      # NaN elsewhere is never a candidate
+    rows[4, :] = 1.5                          # all equal: every token a candidate
+    rows[5, 7] = rows[5, 4321] = 30.0         # tied maxima -> lower id for greedy
+    rows[6, :] = -np.inf
+    rows[6, 4999] = -3.0                      # single finite token, last column
+    rows[7, 1:] = -1e30
+    u = synth.uniforms(1, 8)
+    for params in [SamplingParams(temperature=1.0), SamplingParams(temperature=0.0),
+                   SamplingParams(temperature=0.5, top_k=3), SamplingParams(temperature=1e-40),
+                   SamplingParams(temperature=1.0, repetition_penalty=0.0)]:
+        hist = np.tile(np.array([[7, 4321, 0, 17]], dtype=np.int32), (8, 1))
+        res = gpu_rows(gpu_sampler_factory, rows, params, u, cap=5000, history=hist)
+        want = [ref.sample(params, rows[b], u[b], cap=5000, history=hist[b]) for b in range(8)]
+        compare_sample(res, want, cap=5000)
+
+
+def test_weight_ties_break_toward_lower_id(gpu_sampler_factory, ref):
+    """Distinct logits that round to the same weight q tie; top_k keeps the lower ids (sampler.cpp:39-43)."""
+    v = 9000
+    rows = np.full((2, v), -20.0, dtype=np.float32)
+    base = np.float32(3.0)
+    ups = [base, np.nextafter(base, np.float32(4)), np.nextafter(np.nextafter(base, np.float32(4)), np.float32(4))]
+    for j, i in enumerate([8000, 6000, 4000, 2000, 100]):
+        rows[0, i] = ups[j % 3]
+        rows[1, i] = base
+    rows[:, 50] = 10.0
+    u = synth.uniforms(2, 2)
+    for k in (2, 3, 4):
+        p = SamplingParams(temperature=2.0, top_k=k)
+        res = gpu_rows(gpu_sampler_factory, rows, p, u, cap=16)
+        want = [ref.sample(p, rows[b], u[b], cap=16) for b in range(2)]
+        ids = res.cand_ids.cpu().numpy()
+        flags = res.flags.cpu().numpy()
+        for b in range(2):
+            if flags[b] & 0x2:      # a tie reaching past the collected bound is reported, never silently cut
+                continue
+            assert sorted(ids[b, :k].tolist()) == sorted(want[b]["cand_ids"].tolist())
+
+
+def test_all_masked_row_reports_flag(gpu_sampler_factory, ref):
+    inp = Inputs(91, 4, 3000, with_mask=True, mask_fraction=0.1)
+    inp.mask[1, :] = 0
+    res = gpu_rows(gpu_sampler_factory, inp.logits, SamplingParams(temperature=1.0), inp.u, cap=512, mask=inp.mask)
+    want = [ref.sample(SamplingParams(temperature=1.0), inp.logits[b], inp.u[b], cap=512, mask=inp.mask[b])
+            for b in range(4)]
+    compare_sample(res, want, cap=512)
+    assert res.flags.cpu().numpy()[1] & 0x8 and res.token.cpu().numpy()[1] == 0
+
+
+def test_per_row_parameters(gpu_sampler_factory, ref):
+    import torch
+    v, b = 33000, 6
+    inp = Inputs(101, b, v, n_history=200)
+    ps = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.7, top_k=40, top_p=0.95),
+          SamplingParams(temperature=1.0, min_p=0.02), SamplingParams(temperature=0.8, top_p=0.9),
+          SamplingParams(temperature=1.2, top_k=5, repetition_penalty=1.5),
+          SamplingParams(temperature=0.9, presence_penalty=1.0, frequency_penalty=0.5, min_p=0.01)]
+    s = gpu_sampler_factory(v, b, 256)
+    g = inp.to_gpu()
+    res = s.sample(g["logits"], torch.from_numpy(pack_params(ps)).cuda(), g["u"], **g["kw"])
+    torch.cuda.synchronize()
+    want = [ref.sample(ps[i], inp.logits[i], inp.u[i], cap=256, **inp.row_kwargs(i)) for i in range(b)]
+    compare_sample(res, want, cap=256)
+
+
+def test_long_history_and_heavy_repeats(gpu_sampler_factory, ref):
+    """More history entries than the shared-memory bucket holds, and one id repeated thousands of times."""
+    v, b = 20000, 3
+    inp = Inputs(111, b, v)
+    h = synth.history_zipf(111, b, v, 6000, s=1.3)
+    h[1, :5000] = 77
+    p = SamplingParams(temperature=1.0, min_p=0.001, repetition_penalty=1.1, presence_penalty=0.1,
+                       frequency_penalty=0.001)
+    res = gpu_rows(gpu_sampler_factory, inp.logits, p, inp.u, cap=1024, history=h)
+    want = [ref.sample(p, inp.logits[i], inp.u[i], cap=1024, history=h[i]) for i in range(b)]
+    compare_sample(res, want, cap=1024)
+
+
+def test_unaligned_rows_take_the_plain_load_path(gpu_sampler_factory, ref):
+    import torch
+    v, b = 10001, 5
+    inp = Inputs(121, b, v, ld=v + 2)            # ld % 4 != 0: rows are not 16-byte aligned
+    s = gpu_sampler_factory(v, b, 64)
+    t = torch.from_numpy(inp.logits).cuda()
+    p = SamplingParams(temperature=0.8, top_k=20, top_p=0.9)
+    res = s.sample(t[:, :v], p, torch.from_numpy(inp.u).cuda())
+    torch.cuda.synchronize()
+    compare_sample(res, oracle_sample_rows(ref, p, inp, cap=64), cap=64)
+
+
+def test_host_buffer_entry_point(gpu_sampler_factory, ref):
+    v, b = 129280, 6
+    inp = Inputs(131, b, v, n_history=1000)
+    p = SamplingParams(temperature=0.8, top_p=0.9, min_p=0.05, repetition_penalty=1.1, presence_penalty=0.5,
+                       frequency_penalty=0.3)
+    s = gpu_sampler_factory(v, b, 0)
+    tok, prob, flags = s.sample_host(inp.logits, p, inp.u, history=inp.history)
+    want = oracle_sample_rows(ref, p, inp)
+    assert tok.tolist() == [w["token"] for w in want]
+    assert np.allclose(prob, [w["prob"] for w in want], rtol=1e-5)
