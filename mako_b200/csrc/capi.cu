@@ -36,6 +36,10 @@ int cuda_fail(cudaError_t e, const char* what)
             return cuda_fail(e__, #call);                                                                              \
     } while (0)
 
+// Entries of raw-candidate scratch per row: the vocabulary rounded up to a multiple of 4, so that every row's
+// 12*cap-byte block starts on a 16-byte boundary (the raw candidates are read and written as 8-byte pairs).
+inline uint32_t scratch_cap(uint32_t n_vocab) { return (n_vocab + 3u) & ~3u; }
+
 constexpr uint32_t kPqCap = 1024;      // candidates per list in p/q verification
 constexpr uint32_t kMaxTiles = 1024, kTile = 4096;
 
@@ -44,7 +48,7 @@ constexpr uint32_t kMaxTiles = 1024, kTile = 4096;
 struct mk_sampler {
     int device = 0;
     uint32_t n_vocab = 0, max_batch = 0;
-    uint2* scratch = nullptr;   // [max_batch][n_vocab] raw candidates: a row can never overflow it
+    uint32_t* scratch = nullptr; // [max_batch][3*n_vocab] words: raw candidates (a row can never overflow it) + a float per column
     // p/q verification lists
     int32_t *p_ids = nullptr, *q_ids = nullptr;
     float *p_q = nullptr, *q_q = nullptr, *p_total = nullptr, *q_total = nullptr, *q_prob = nullptr;
@@ -122,7 +126,7 @@ void fill_common(mk::RowKernelArgs& a, const mk_sampler* s, const mk_rows* r)
     a.params_dev = r->params_dev;
     a.params = r->params;
     a.scratch = s->scratch;
-    a.scratch_cap = s->n_vocab;
+    a.scratch_cap = scratch_cap(s->n_vocab);
     a.use_bulk_copy = ((reinterpret_cast<uintptr_t>(r->logits) & 15u) == 0 && (r->ld % 4u) == 0) ? 1 : 0;
 }
 
@@ -216,7 +220,7 @@ int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t m
         if (e == cudaSuccess)
             e = cudaMalloc(p, bytes);
     };
-    alloc((void**)&s->scratch, b * (size_t)n_vocab * sizeof(uint2));
+    alloc((void**)&s->scratch, b * (size_t)scratch_cap(n_vocab) * 12);
     alloc((void**)&s->p_ids, b * kPqCap * 4);
     alloc((void**)&s->q_ids, b * kPqCap * 4);
     alloc((void**)&s->p_q, b * kPqCap * 4);

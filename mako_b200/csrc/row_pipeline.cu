@@ -69,6 +69,7 @@ struct __align__(128) Smem {
 struct RowCfg {
     float temperature, inv_t, minp_eff, top_p;
     uint32_t top_k;
+    uint32_t hist_k;    // the histogram bound keeps the hist_k largest elements
     float rep, presence, frequency;
     bool greedy, hist_mode, need_sum, use_topp, pen_active;
     float delta_w;      // keep elements with l >= running max - delta_w
@@ -98,13 +99,17 @@ __device__ __forceinline__ RowCfg make_cfg(const mk_sampling_params& p, uint32_t
     c.pen_active = !(c.rep == 1.0f && c.presence == 0.0f && c.frequency == 0.0f);
     c.use_topp = p.top_p < 1.0f;
     c.hist_mode = !c.greedy && p.top_k > 0 && p.top_k < n_vocab;
+    // One more than top_k is kept, so that "more candidates than top_k" (which decides whether the reference
+    // truncates, and with it the order of the list, sampler.cpp:39) can be told from the kept elements alone.
+    c.hist_k = p.top_k + 1u;
     const bool minp_on = c.minp_eff > 0.0f;
     // The float total over "all candidates" is only needed when top_p is the only truncation.
     c.need_sum = !c.greedy && c.use_topp && !minp_on && !c.hist_mode;
-    c.force_none = !(c.inv_t < __int_as_float(0x7f800000)) || !(c.inv_t == c.inv_t);
+    c.force_none = !c.greedy && (!(c.inv_t < __int_as_float(0x7f800000)) || !(c.inv_t == c.inv_t));
     if (mode == kModeVpLocal) {
         c.hist_mode = vp_k < n_vocab;
         c.top_k = vp_k;
+        c.hist_k = vp_k;
         c.need_sum = true;
         c.use_topp = false;
         c.minp_eff = 0.0f;
@@ -206,7 +211,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
     const bool has_fix = has_hist || nb > 0;
     const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
-    uint2* __restrict__ scratch = a.scratch + (size_t)row * a.scratch_cap;
+    // Per-row scratch: scratch_cap raw candidates (logit bits, column), then scratch_cap floats indexed by column
+    // that the large-list path uses.
+    uint2* __restrict__ scratch = reinterpret_cast<uint2*>(a.scratch + (size_t)row * 3u * a.scratch_cap);
+    float* __restrict__ qrow = reinterpret_cast<float*>(a.scratch + (size_t)row * 3u * a.scratch_cap + 2u * a.scratch_cap);
 
     // ---- set-up -------------------------------------------------------------------------------------------------
     if (tid == 0) {
@@ -398,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         uint64_t* const avail = has_fix ? s.ready : s.full;
         const float c2 = cfg.inv_t * 1.4426950408889634f;
         const float ninf = -__int_as_float(0x7f800000);
-        const bool collect = !cfg.greedy;
+        const bool collect = !cfg.greedy || a.mode == kModeVpLocal;
         float warp_pub = ninf;
         for (uint32_t t = 0; t < n_tiles; ++t) {
             const uint32_t st = t % kStages, k = t / kStages;
@@ -505,7 +513,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                             if ((int)lane + o < 32)
                                 suf += y;
                         }
-                        const uint32_t hit = __ballot_sync(0xffffffffu, cum + suf >= cfg.top_k);
+                        const uint32_t hit = __ballot_sync(0xffffffffu, cum + suf >= cfg.hist_k);
                         if (hit)
                             found = g * 32 + (31 - __clz(hit));
                         cum += __shfl_sync(0xffffffffu, suf, 0);
@@ -585,19 +593,24 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (a.mode == kModeVpLocal) {
         // Shard record: header {max, n, sum} then the k best (logit, global id), by (logit desc, id asc).
         unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
-        const uint32_t n_raw = min(s.ncand, min(a.scratch_cap, (uint32_t)kSortCap));
-        const bool over = s.ncand > min(a.scratch_cap, (uint32_t)kSortCap);
+        const uint32_t n_all = min(s.ncand, a.scratch_cap);
+        const float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        for (uint32_t i = tid; i < n_all; i += kThreads) {
+            const uint2 c = scratch[i];
+            if (__uint_as_float(c.x) >= thr_final) {
+                const uint32_t slot = atomicAdd(&s.nsurv, 1u);
+                if (slot < (uint32_t)kSortCap)
+                    keys[slot] = ((unsigned long long)(~order_key(__uint_as_float(c.x))) << 32) | c.y;
+            }
+        }
+        __syncthreads();
+        const uint32_t n_raw = min(s.nsurv, (uint32_t)kSortCap);
+        const bool over = s.nsurv > (uint32_t)kSortCap || s.ncand > a.scratch_cap;
         uint32_t n2 = 2;
         while (n2 < n_raw)
             n2 <<= 1;
-        for (uint32_t i = tid; i < n2; i += kThreads) {
-            unsigned long long key = ~0ull;
-            if (i < n_raw) {
-                const uint2 c = scratch[i];
-                key = ((unsigned long long)(~order_key(__uint_as_float(c.x))) << 32) | c.y;
-            }
-            keys[i] = key;
-        }
+        for (uint32_t i = n_raw + tid; i < n2; i += kThreads)
+            keys[i] = ~0ull;
         __syncthreads();
         block_sort(keys, n2);
         unsigned char* rec = reinterpret_cast<unsigned char*>(a.vp_records) + (size_t)row * vp_record_bytes(a.vp_k);
@@ -645,7 +658,68 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     bool overflow = s.ncand > a.scratch_cap;
     if (!s.nan0) {
         // Elements collected while the running maximum was still low are dropped by the final bound first.
-        const float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        if (cfg.need_sum && n_raw > 1024u) {
+            // top_p alone: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was not
+            // collected belongs to that tail; collected elements can join it from the bottom for as long as the
+            // tail stays within the budget. Approximate weights decide the cut (with margins); the nucleus itself
+            // is then computed from exact weights, and a cut that turns out too tight is reported.
+            float* fh = reinterpret_cast<float*>(s.hist);
+            for (uint32_t i = tid; i < kBins; i += kThreads)
+                fh[i] = 0.0f;
+            if (tid == 0)
+                s.warp_sum[0] = 0.0;
+            __syncthreads();
+            const float c2 = cfg.inv_t * 1.4426950408889634f;
+            double mine = 0.0;
+            for (uint32_t i = tid; i < n_raw; i += kThreads) {
+                const float w = __uint_as_float(scratch[i].x);
+                if (w >= thr_final) {
+                    const float qa = exp2f((w - m) * c2);
+                    atomicAdd(&fh[order_key(w) >> kBinShift], qa);
+                    mine += (double)qa;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                mine += __shfl_xor_sync(0xffffffffu, mine, o);
+            if (lane == 0)
+                atomicAdd(&s.warp_sum[0], mine);
+            __syncthreads();
+            if (warp == 0) {
+                const double collected = s.warp_sum[0];
+                const double budget = (1.0 - (double)cfg.top_p) * total_approx * 0.999 -
+                                      (fmax(total_approx - collected, 0.0) + 1e-5 * total_approx);
+                double cum = 0.0;
+                int cut = 0; // elements in bins below `cut` may be dropped
+                bool stop = false;
+                for (int g = 0; g < kBins / 32 && !stop; ++g) {
+                    const float v = fh[g * 32 + lane];
+                    double pre = (double)v; // inclusive prefix over lanes
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const double y = __shfl_up_sync(0xffffffffu, pre, o);
+                        if ((int)lane >= o)
+                            pre += y;
+                    }
+                    const uint32_t okm = __ballot_sync(0xffffffffu, cum + pre <= budget);
+                    if (okm == 0xffffffffu) {
+                        cut = (g + 1) * 32;
+                        cum += __shfl_sync(0xffffffffu, pre, 31);
+                    } else {
+                        cut = g * 32 + __ffs(~okm) - 1; // first bin that no longer fits
+                        stop = true;
+                    }
+                }
+                if (lane == 0 && budget > 0.0 && cut > 0 && cut < kBins) {
+                    const float edge = key_to_float((uint32_t)cut << kBinShift);
+                    if (edge == edge)
+                        s.thr_topk_bits = __float_as_uint(fmaxf(__uint_as_float(s.thr_topk_bits), edge));
+                }
+            }
+            __syncthreads();
+            thr_final = fmaxf(thr_final, __uint_as_float(s.thr_topk_bits));
+        }
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
             const uint2 c = scratch[i];
             if (!(__uint_as_float(c.x) >= thr_final))
@@ -661,6 +735,134 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     __syncthreads();
     uint32_t n = s.nsurv;
+    if (!overflow && n > (uint32_t)kSortCap && !cfg.use_topp && !(cfg.top_k > 0 && cfg.top_k < n)) {
+        // More candidates than the shared-memory sort holds, and no truncation orders them: the draw walks them
+        // in ascending id (sampler.cpp:64-73). The exact weights are laid out by column in scratch and one thread
+        // adds and walks them in the reference's order and precision; the other threads stage tiles for it.
+        const float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        for (uint32_t i = tid; i < V; i += kThreads)
+            qrow[i] = 0.0f;
+        __syncthreads();
+        for (uint32_t i = tid; i < n_raw; i += kThreads) {
+            const uint2 c = scratch[i];
+            if (!(__uint_as_float(c.x) >= thr_final))
+                continue;
+            const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
+            if (q >= cfg.minp_eff && q > 0.0f)
+                qrow[c.y] = q;
+        }
+        __threadfence_block();
+        __syncthreads();
+        float* stage = &s.ring[0][0];
+        const int32_t draft_col = (a.mode == kModeVerify) ? (a.draft[row] - a.id_offset) : -1;
+        float total = 0.0f, q_draft = 0.0f;
+        // pass 0: float total (and the draft's weight); pass 1: the walk
+        float r = 0.0f, walk_total = 0.0f, eps = 0.0f;
+        int32_t tok = -1, last = -1, acc = 0;
+        float prob = 0.0f, last_q = 0.0f;
+        bool first = true, done = false, skip_draft = false;
+        uint32_t emitted = 0;
+        for (int pass = 0; pass < 2 && !done; ++pass) {
+            for (uint32_t t = 0; t * kTile < V && !done; ++t) {
+                const uint32_t base = t * kTile, n_t = min((uint32_t)kTile, V - base);
+                float* buf = stage + (t & 1) * kTile;
+                for (uint32_t e = tid; e < n_t; e += kThreads)
+                    buf[e] = qrow[base + e];
+                __syncthreads();
+                if (tid == 0) {
+                    if (pass == 0) {
+                        for (uint32_t e = 0; e < n_t; ++e) {
+                            const float q = buf[e];
+                            if (q > 0.0f) {
+                                total = __fadd_rn(total, q);
+                                if ((int32_t)(base + e) == draft_col)
+                                    q_draft = q;
+                                if (emitted < a.cand_cap) {
+                                    if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + emitted] = (int32_t)(base + e) + a.id_offset;
+                                    if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + emitted] = q;
+                                }
+                                ++emitted;
+                            }
+                        }
+                    } else {
+                        for (uint32_t e = 0; e < n_t && !done; ++e) {
+                            const float q = buf[e];
+                            if (!(q > 0.0f) || (skip_draft && (int32_t)(base + e) == draft_col))
+                                continue;
+                            last = (int32_t)(base + e);
+                            last_q = q;
+                            if (r < q) {
+                                tok = last;
+                                prob = __fdiv_rn(q, walk_total);
+                                if ((!first && r < eps) || __fsub_rn(q, r) < eps)
+                                    s.flags = 1; // upper boundary: cleared below if this was the last candidate
+                                s.n_final = (!first && r < eps) ? 2u : 0u;
+                                done = true;
+                            } else {
+                                r = __fsub_rn(r, q);
+                                first = false;
+                            }
+                        }
+                    }
+                }
+                __syncthreads();
+                if (pass == 1) {
+                    // the walking thread publishes "done" through shared memory
+                    if (tid == 0)
+                        s.nsurv = done ? 0xffffffffu : n;
+                    __syncthreads();
+                    done = s.nsurv == 0xffffffffu;
+                }
+            }
+            if (pass == 0) {
+                // decide what the walk does (sampler.cpp:100-106 for verify)
+                if (tid == 0) {
+                    walk_total = total;
+                    if (a.mode == kModeVerify) {
+                        acc = __fmul_rn(a.u[row], total) < q_draft;
+                        if (acc) {
+                            tok = draft_col + a.id_offset;
+                            prob = __fdiv_rn(q_draft, total);
+                        } else {
+                            skip_draft = true;
+                            walk_total = __fsub_rn(total, q_draft);
+                        }
+                    }
+                    const float uu = (a.mode == kModeVerify) ? a.u2[row] : (a.u ? a.u[row] : 0.0f);
+                    r = __fmul_rn(uu, walk_total);
+                    eps = 1e-6f * walk_total;
+                    s.n_final = 0;
+                    s.flags = 0;
+                    s.nsurv = (a.mode == kModeDistOnly || acc) ? 0xffffffffu : n;
+                }
+                __syncthreads();
+                done = s.nsurv == 0xffffffffu;
+            }
+        }
+        if (tid == 0) {
+            if (a.mode == kModeDistOnly) {
+                tok = -1;
+            } else if (tok < 0) { // rounding: the last candidate
+                tok = last;
+                prob = __fdiv_rn(last_q, walk_total);
+            } else if (!acc && a.mode != kModeDistOnly) {
+                // near-boundary report: lower boundary always counts; the upper one only if a candidate follows
+                bool more = false;
+                for (uint32_t c = (uint32_t)tok + 1; c < V && !more; ++c)
+                    if (qrow[c] > 0.0f && !(skip_draft && (int32_t)c == draft_col))
+                        more = true;
+                if (s.n_final == 2u || (s.flags && more))
+                    flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
+            }
+            if (a.token) a.token[row] = (tok >= 0 && !(acc)) ? tok + a.id_offset : tok;
+            if (a.prob) a.prob[row] = prob;
+            if (a.flags) a.flags[row] = flags;
+            if (a.n_cand) a.n_cand[row] = n;
+            if (a.accepted) a.accepted[row] = acc;
+            if (a.total_out) a.total_out[row] = total;
+        }
+        return;
+    }
     if (n > (uint32_t)kSortCap)
         overflow = true;
     if (overflow) {

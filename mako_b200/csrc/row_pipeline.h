@@ -48,7 +48,7 @@ struct RowKernelArgs {
     void* vp_records;
     uint32_t vp_k;
     // scratch owned by the handle
-    uint2* scratch;        // [batch][scratch_cap] raw candidates (logit bits, column)
+    uint32_t* scratch;     // [batch][3*scratch_cap] words: raw candidates (logit bits, column), then a float per column
     uint32_t scratch_cap;
     int mode;
     int use_bulk_copy;     // 1: TMA bulk staging (aligned rows); 0: plain loads

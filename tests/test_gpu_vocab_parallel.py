@@ -39,10 +39,14 @@ def test_vocab_parallel_equals_single_device(gpu_sampler_factory, ref, n_shards,
     exact = 0
     for i in range(b):
         w = ref.sample(params, inp.logits[i], inp.u[i], cap=128, history=inp.history[i])
-        if flags[i] & (0x20 | 0x2):
-            continue  # reported: the nucleus may reach past a shard's list, or a decision sat in the guard band
+        if flags[i] & 0x20:
+            # reported: the nucleus may reach past a shard's list — only legitimate when it is larger than one list
+            assert w["n_cand"] > k, f"row {i} flagged with a nucleus of {w['n_cand']}"
+            continue
+        if flags[i] & 0x2:
+            continue  # a decision sat in the guard band of the rescaled partial sums
         assert tok[i] == w["token"], f"row {i}"
         assert ncand[i] == w["n_cand"]
         assert np.array_equal(ids[i, :ncand[i]], w["cand_ids"][:ncand[i]])
         exact += 1
-    assert exact >= b - 1
+    assert exact >= b - 3
