@@ -41,7 +41,7 @@ int cuda_fail(cudaError_t e, const char* what)
 inline uint32_t scratch_cap(uint32_t n_vocab) { return (n_vocab + 3u) & ~3u; }
 
 constexpr uint32_t kPqCap = 1024;      // candidates per list in p/q verification
-constexpr uint32_t kMaxTiles = 1024, kTile = 4096;
+constexpr uint32_t kMaxTiles = 512, kTile = 4096;
 
 } // namespace
 
@@ -56,6 +56,8 @@ struct mk_sampler {
     int32_t* p_tok = nullptr;
     // host-buffer staging (sized on first use)
     cudaStream_t own_stream = nullptr;
+    uint32_t dbg = 0;
+    unsigned long long* timing = nullptr; // debug: per-row phase timestamps of the next launches
     unsigned char* stage = nullptr;
     size_t stage_bytes = 0;
 };
@@ -127,6 +129,8 @@ void fill_common(mk::RowKernelArgs& a, const mk_sampler* s, const mk_rows* r)
     a.params = r->params;
     a.scratch = s->scratch;
     a.scratch_cap = scratch_cap(s->n_vocab);
+    a.timing = s->timing;
+    a.dbg = s->dbg;
     a.use_bulk_copy = ((reinterpret_cast<uintptr_t>(r->logits) & 15u) == 0 && (r->ld % 4u) == 0) ? 1 : 0;
 }
 
@@ -486,6 +490,22 @@ int mk_sampler_sample_host(mk_sampler* s, const mk_rows* hr, const float* u, con
     if (ho->n_cand)
         MK_CUDA(cudaMemcpyAsync(ho->n_cand, dout.n_cand, B * 4, cudaMemcpyDeviceToHost, st));
     MK_CUDA(cudaStreamSynchronize(st));
+    return MK_OK;
+}
+
+int mk_debug_set_flags(mk_sampler* s, uint32_t flags)
+{
+    if (!s)
+        return fail(MK_ERR_INVALID_ARGUMENT, "null sampler handle");
+    s->dbg = flags;
+    return MK_OK;
+}
+
+int mk_debug_set_timing(mk_sampler* s, unsigned long long* timing_dev)
+{
+    if (!s)
+        return fail(MK_ERR_INVALID_ARGUMENT, "null sampler handle");
+    s->timing = timing_dev;
     return MK_OK;
 }
 

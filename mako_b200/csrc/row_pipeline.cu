@@ -32,31 +32,34 @@ namespace mk {
 
 namespace {
 
-constexpr int kTile = 4096;   // floats per tile
-constexpr int kStages = 4;
+constexpr int kTile = 4096;   // floats per tile (16 KB)
+constexpr int kStages = 3;
 constexpr int kProducerThreads = 32;
 constexpr int kFixers = 64;
 constexpr int kReaders = 256;
 constexpr int kThreads = kProducerThreads + kFixers + kReaders;
 constexpr int kReaderWarps = kReaders / 32;
-constexpr int kHistCap = 4096;  // history entries bucketed in shared memory; longer histories scan global memory
-constexpr int kMaxTiles = 1024; // n_vocab <= 4 Mi columns
-constexpr int kSortCap = kStages * kTile * 4 / 8; // 8192 64-bit sort keys fit in the ring
+constexpr int kHistCap = 4096;  // history entries de-duplicated in shared memory; longer histories scan global memory
+constexpr int kBmWords = 5120;  // history bitmap: one bit per column, vocabularies up to 163840 columns
+constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
+constexpr int kSortCap = 8192;  // 64-bit sort keys: the ring and the history bitmap/prefix behind it (78 KB) hold them
+constexpr int kCandSmem = 2048;
 constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = 21;
 constexpr uint32_t kBarFix = 1, kBarRead = 2;
 
 struct __align__(128) Smem {
-    float ring[kStages][kTile];
-    uint32_t cnt[kTile / 2];        // per-tile id counts, two 16-bit counters per word
-    uint16_t hs[kHistCap];          // history as column-within-tile, bucketed by tile
-    uint32_t hstart[kMaxTiles + 1]; // bucket boundaries
+    float ring[kStages][kTile];     // tile ring; after the streaming, with `table`, the sort area of the finish
+    uint32_t bitmap[kBmWords];      // bit c set: column c was generated (long histories: per-tile id counters)
+    uint16_t prefix[kBmWords];      // number of set bits in the words before this one = rank of its first set bit
+    uint32_t counts[kHistCap / 2];  // occurrences per distinct generated column, by rank, two 16-bit counters a word
     uint32_t hist[kBins];           // top_k: counts per key bin
-    double warp_sum[kReaderWarps];
+    uint2 cbuf[kCandSmem];          // the first raw candidates (logit bits, column); later ones go to global scratch
+    double warp_sum[kThreads / 32];
     uint64_t full[kStages], ready[kStages], empty[kStages];
     unsigned long long best_key;    // (order key of the row maximum << 32) | ~column: first argmax wins
     uint32_t m_key;                 // running maximum, as order key
-    uint32_t thr_topk_bits;         // top_k lower bound (float bits)
+    uint32_t thr_topk_key;          // top_k lower bound, as order key (only ever raised)
     uint32_t ncand;                 // raw candidates appended
     uint32_t nsurv;                 // candidates surviving the exact filter
     uint32_t abort_flag;
@@ -75,6 +78,13 @@ struct RowCfg {
     float delta_w;      // keep elements with l >= running max - delta_w
     bool force_none;    // inv_t is inf/NaN: no finite weight can exist
 };
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ float warp_max(float v)
 {
@@ -206,17 +216,33 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const bool has_hist = !cfg.greedy && cfg.pen_active && hlen_all > 0;
     const uint32_t hlen = has_hist ? hlen_all : 0u;
     const int32_t* __restrict__ hrow = a.history ? a.history + (size_t)row * a.history_ld : nullptr;
-    const bool long_history = hlen > (uint32_t)kHistCap;
+    const bool long_history = hlen > (uint32_t)kHistCap || V > kMaxBitmapVocab;
     const uint32_t nb = a.bias ? a.n_bias : 0u;
     const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
-    const bool has_fix = has_hist || nb > 0;
+    const bool has_fix = nb > 0 || has_hist; // work for the fix-up warps
     const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
     // Per-row scratch: scratch_cap raw candidates (logit bits, column), then scratch_cap floats indexed by column
     // that the large-list path uses.
     uint2* __restrict__ scratch = reinterpret_cast<uint2*>(a.scratch + (size_t)row * 3u * a.scratch_cap);
     float* __restrict__ qrow = reinterpret_cast<float*>(a.scratch + (size_t)row * 3u * a.scratch_cap + 2u * a.scratch_cap);
 
+    const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
+    const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
+    const int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
+    // The history is read into registers first thing, all loads in flight together, so that their latency
+    // overlaps the barrier set-up instead of being paid once per loop trip.
+    constexpr int kHistPerThread = (kHistCap + kThreads - 1) / kThreads;
+    int32_t hv[kHistPerThread];
+    if (has_hist && !long_history) { // = use_table
+#pragma unroll
+        for (int i = 0; i < kHistPerThread; ++i) {
+            const uint32_t j = (uint32_t)i * kThreads + tid;
+            hv[i] = (j < hlen) ? __ldg(hrow + j) : 0;
+        }
+    }
     // ---- set-up -------------------------------------------------------------------------------------------------
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 0] = global_ns();
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
@@ -225,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
         s.best_key = 0ull;
         s.m_key = order_key(-__int_as_float(0x7f800000));
-        s.thr_topk_bits = __float_as_uint(-FLT_MAX);
+        s.thr_topk_key = order_key(-FLT_MAX);
         s.ncand = 0;
         s.nsurv = 0;
         s.abort_flag = 0;
@@ -235,66 +261,107 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         s.flags = 0;
         fence_barrier_init();
     }
-    for (uint32_t i = tid; i < kTile / 2; i += kThreads)
-        s.cnt[i] = 0;
+    uint32_t* const cnt = s.bitmap; // long histories: per-tile id counters (two 16-bit counters per word)
+    const bool use_table = has_hist && !long_history;
+    const uint32_t bm_words = (V + 31u) / 32u;
+    if (long_history)
+        for (uint32_t i = tid; i < kTile / 2; i += kThreads)
+            cnt[i] = 0;
     if (cfg.hist_mode)
         for (uint32_t i = tid; i < kBins; i += kThreads)
             s.hist[i] = 0;
-    if (has_hist && !long_history)
-        for (uint32_t i = tid; i <= n_tiles; i += kThreads)
-            s.hstart[i] = 0;
+    if (use_table) {
+        for (uint32_t i = tid; i < bm_words; i += kThreads)
+            s.bitmap[i] = 0;
+        for (uint32_t i = tid; i < kHistCap / 2; i += kThreads)
+            s.counts[i] = 0;
+    }
+    uint32_t tiles_issued = 0;
     __syncthreads();
-
-    if (has_hist && !long_history) {
-        // Bucket the history by tile: count, exclusive scan, scatter (counting sort on column / kTile).
-        for (uint32_t j = tid; j < hlen; j += kThreads) {
-            const int64_t col = (int64_t)hrow[j] - a.id_offset;
-            if (col >= 0 && col < (int64_t)V)
-                atomicAdd(&s.hstart[(uint32_t)col / kTile + 1], 1u);
-        }
-        __syncthreads();
-        if (warp == 0) {
-            uint32_t carry = 0;
-            for (uint32_t base = 0; base <= n_tiles; base += 32) {
-                const uint32_t i = base + lane;
-                uint32_t v = (i <= n_tiles) ? s.hstart[i] : 0u;
-                uint32_t x = v;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
-                    if ((int)lane >= o)
-                        x += y;
+    // The producer fills the ring before anything else, so that the copies fly during the set-up.
+    if (a.use_bulk_copy) {
+        tiles_issued = min((uint32_t)kStages, n_tiles);
+        if (tid == 0) {
+            for (uint32_t t = 0; t < tiles_issued; ++t) {
+                const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
+                const uint32_t bytes = (n_t * 4u) & ~15u;
+                const float* src = lrow + (size_t)t * kTile;
+                for (uint32_t e = bytes / 4; e < n_t; ++e)
+                    s.ring[t][e] = src[e];
+                if (bytes > 0) {
+                    mbar_arrive_expect_tx(&s.full[t], bytes);
+                    bulk_load(s.ring[t], src, bytes, &s.full[t]);
+                } else {
+                    mbar_arrive(&s.full[t]);
                 }
-                if (i <= n_tiles)
-                    s.hstart[i] = carry + x; // inclusive: hstart[t+1] = entries in tiles 0..t
-                carry += __shfl_sync(0xffffffffu, x, 31);
+            }
+        }
+    }
+    if (use_table) {
+        // The generated tokens as the reference keeps them (a multiset id -> count, sampler.cpp:15-18), in a form
+        // the readers can consult per column without searching: a bitmap of generated columns, the number of set
+        // bits before each bitmap word (so a column's rank among the distinct ones is one popcount away), and the
+        // counts by rank.
+#pragma unroll
+        for (int hi = 0; hi < kHistPerThread; ++hi) {
+            const uint32_t j = (uint32_t)hi * kThreads + tid;
+            const int64_t col64 = (j < hlen) ? ((int64_t)hv[hi] - a.id_offset) : -1;
+            if (col64 >= 0 && col64 < (int64_t)V) {
+                const uint32_t col = (uint32_t)col64, bit = 1u << (col & 31u);
+                if (!(*(volatile uint32_t*)&s.bitmap[col >> 5] & bit)) // skip the atomic once the bit is visible
+                    atomicOr(&s.bitmap[col >> 5], bit);
             }
         }
         __syncthreads();
-        // hstart[t] now holds the END of bucket t-1 = START of bucket t (hstart[0] = 0). Scatter with the
-        // tile's own 16-bit counters as cursors (they are free until the streaming starts), then clear them.
-        for (uint32_t j = tid; j < hlen; j += kThreads) {
-            const int64_t col = (int64_t)hrow[j] - a.id_offset;
-            if (col >= 0 && col < (int64_t)V) {
-                const uint32_t t = (uint32_t)col / kTile;
-                const uint32_t pos = s.hstart[t] + atomicAdd(&s.cnt[t], 1u);
-                s.hs[pos] = (uint16_t)((uint32_t)col % kTile);
+        {
+            // exclusive prefix of the per-word popcounts: each thread takes a contiguous run of words
+            const uint32_t per = (bm_words + kThreads - 1) / kThreads;
+            const uint32_t w0 = min(tid * per, bm_words), w1 = min(w0 + per, bm_words);
+            uint32_t mine = 0;
+            for (uint32_t w = w0; w < w1; ++w)
+                mine += __popc(s.bitmap[w]);
+            uint32_t inc = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+                if ((int)lane >= o)
+                    inc += y;
+            }
+            uint32_t* wtot = reinterpret_cast<uint32_t*>(s.warp_sum); // 16 words of scratch
+            if (lane == 31)
+                wtot[warp] = inc;
+            __syncthreads();
+            uint32_t before = inc - mine;
+            for (uint32_t w = 0; w < warp; ++w)
+                before += wtot[w];
+            for (uint32_t w = w0; w < w1; ++w) {
+                s.prefix[w] = (uint16_t)before;
+                before += __popc(s.bitmap[w]);
             }
         }
         __syncthreads();
-        for (uint32_t i = tid; i < n_tiles; i += kThreads)
-            s.cnt[i] = 0;
+#pragma unroll
+        for (int hi = 0; hi < kHistPerThread; ++hi) {
+            const uint32_t j = (uint32_t)hi * kThreads + tid;
+            const int64_t col64 = (j < hlen) ? ((int64_t)hv[hi] - a.id_offset) : -1;
+            if (col64 >= 0 && col64 < (int64_t)V) {
+                const uint32_t col = (uint32_t)col64;
+                const uint32_t rank = s.prefix[col >> 5] + __popc(s.bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
+                atomicAdd(&s.counts[rank >> 1], 1u << ((rank & 1u) * 16u));
+            }
+        }
         __syncthreads();
     }
-
     // ---- streaming ----------------------------------------------------------------------------------------------
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 1] = global_ns();
     float best = -__int_as_float(0x7f800000);
     int32_t best_col = -1;
     double sum_acc = 0.0; // sum of exp2((l - best) * c2) over this thread's elements (need_sum)
 
     if (warp == 0) {
         // producer
-        for (uint32_t t = 0; t < n_tiles; ++t) {
+        for (uint32_t t = tiles_issued; t < n_tiles; ++t) {
             const uint32_t st = t % kStages, k = t / kStages;
             float* dst = s.ring[st];
             const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
@@ -356,37 +423,36 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     if (has_hist)
                         named_barrier(kBarFix, kFixers);
                 }
-                if (has_hist) {
-                    if (!long_history) {
-                        const uint32_t e0 = s.hstart[t], e1 = s.hstart[t + 1];
-                        if (e1 > e0) {
-                            for (uint32_t e = e0 + ft; e < e1; e += kFixers) {
-                                const uint32_t loc = s.hs[e];
-                                atomicAdd(&s.cnt[loc >> 1], 1u << ((loc & 1u) * 16u));
-                            }
-                            named_barrier(kBarFix, kFixers);
-                            for (uint32_t e = e0 + ft; e < e1; e += kFixers) {
-                                const uint32_t loc = s.hs[e];
-                                const uint32_t sh = (loc & 1u) * 16u;
-                                // Claim: the first thread to clear the counter owns the id and its count.
-                                const uint32_t old = atomicAnd(&s.cnt[loc >> 1], ~(0xffffu << sh));
-                                const uint32_t n = (old >> sh) & 0xffffu;
-                                if (n)
-                                    tp[loc] = penalise(tp[loc], n, cfg);
-                            }
+                if (use_table) {
+                    // penalties (sampler.cpp:23-28): the tile's generated columns are the set bits of its bitmap
+                    // words; a column's rank among all generated columns indexes its count. Each column is touched
+                    // by exactly one thread.
+                    const uint32_t w_begin = base >> 5, w_end = min((base + n_t + 31u) >> 5, bm_words);
+                    for (uint32_t wd = w_begin + ft; wd < w_end; wd += kFixers) {
+                        uint32_t bits = s.bitmap[wd];
+                        uint32_t rank = s.prefix[wd];
+                        while (bits) {
+                            const uint32_t bpos = __ffs(bits) - 1;
+                            bits &= bits - 1;
+                            const uint32_t loc = (wd << 5) + bpos - base;
+                            const uint32_t n = (s.counts[rank >> 1] >> ((rank & 1u) * 16u)) & 0xffffu;
+                            ++rank;
+                            tp[loc] = penalise(tp[loc], n, cfg);
                         }
-                    } else {
+                    }
+                } else if (has_hist) {
+                    {
                         for (uint32_t j = ft; j < hlen; j += kFixers) {
                             const int64_t loc = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
                             if (loc >= 0 && loc < (int64_t)n_t)
-                                atomicAdd(&s.cnt[(uint32_t)loc >> 1], 1u << (((uint32_t)loc & 1u) * 16u));
+                                atomicAdd(&cnt[(uint32_t)loc >> 1], 1u << (((uint32_t)loc & 1u) * 16u));
                         }
                         named_barrier(kBarFix, kFixers);
                         for (uint32_t j = ft; j < hlen; j += kFixers) {
                             const int64_t loc64 = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
                             if (loc64 >= 0 && loc64 < (int64_t)n_t) {
                                 const uint32_t loc = (uint32_t)loc64, sh = (loc & 1u) * 16u;
-                                const uint32_t old = atomicAnd(&s.cnt[loc >> 1], ~(0xffffu << sh));
+                                const uint32_t old = atomicAnd(&cnt[loc >> 1], ~(0xffffu << sh));
                                 const uint32_t n = (old >> sh) & 0xffffu;
                                 if (n)
                                     tp[loc] = penalise(tp[loc], n, cfg);
@@ -490,7 +556,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             if (cfg.hist_mode) {
                 // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
                 // where the count from the top reaches k bounds the k-th largest from below.
-                thr = fmaxf(thr, __uint_as_float(*(volatile uint32_t*)&s.thr_topk_bits));
+                thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
                 if (tm >= thr) {
 #pragma unroll
                     for (int e = 0; e < 16; ++e)
@@ -518,24 +584,23 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                             found = g * 32 + (31 - __clz(hit));
                         cum += __shfl_sync(0xffffffffu, suf, 0);
                     }
-                    if (lane == 0 && found >= 0) {
-                        const float edge = key_to_float((uint32_t)found << kBinShift);
-                        // the lowest key of a bin is its smallest float; NaN keys (bin 0) never get here
-                        if (edge == edge)
-                            s.thr_topk_bits = __float_as_uint(fmaxf(edge, -FLT_MAX));
-                    }
+                    // the lowest key of a bin is its smallest float; bin 0 (NaN keys) is never a bound
+                    if (lane == 0 && found > 0)
+                        s.thr_topk_key = max(s.thr_topk_key, (uint32_t)found << kBinShift);
                 }
                 named_barrier(kBarRead, kReaders);
-                thr = fmaxf(thr, __uint_as_float(*(volatile uint32_t*)&s.thr_topk_bits));
+                thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
             }
             if (collect && tm >= thr) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e)
                     if (w[e] >= thr) {
                         const uint32_t slot = atomicAdd(&s.ncand, 1u);
-                        if (slot < a.scratch_cap)
-                            scratch[slot] =
-                                make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                        const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                        if (slot < (uint32_t)kCandSmem)
+                            s.cbuf[slot] = c;
+                        else if (slot < a.scratch_cap)
+                            scratch[slot] = c;
                     }
             }
         }
@@ -546,6 +611,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     __syncthreads();
 
     // ---- finish -------------------------------------------------------------------------------------------------
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 2] = global_ns();
     if (s.abort_flag) {
         // A bounded wait ran out. Give copies still in flight time to land before the CTA's shared memory is
         // released, then report.
@@ -583,10 +650,16 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             for (int o = 16; o > 0; o >>= 1)
                 part += __shfl_xor_sync(0xffffffffu, part, o);
             if (lane == 0)
-                s.warp_sum[warp - 1 - kFixers / 32] = part;
+                s.warp_sum[warp] = part;
+        } else {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0)
+                s.warp_sum[warp] = part;
         }
         __syncthreads();
-        for (int i = 0; i < kReaderWarps; ++i)
+        for (int i = 0; i < kThreads / 32; ++i)
             total_approx += s.warp_sum[i];
     }
 
@@ -594,9 +667,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // Shard record: header {max, n, sum} then the k best (logit, global id), by (logit desc, id asc).
         unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
         const uint32_t n_all = min(s.ncand, a.scratch_cap);
-        const float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         for (uint32_t i = tid; i < n_all; i += kThreads) {
-            const uint2 c = scratch[i];
+            const uint2 c = (i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i];
             if (__uint_as_float(c.x) >= thr_final) {
                 const uint32_t slot = atomicAdd(&s.nsurv, 1u);
                 if (slot < (uint32_t)kSortCap)
@@ -647,7 +720,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             if (a.cand_q && a.cand_cap) a.cand_q[(size_t)row * a.cand_cap] = 1.0f;
             if (a.total_out) a.total_out[row] = 1.0f;
             if (a.mode == kModeVerify && a.accepted)
-                a.accepted[row] = (a.draft[row] == t) ? 1 : 0;
+                a.accepted[row] = (draft_row == t) ? 1 : 0;
         }
         return;
     }
@@ -658,7 +731,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     bool overflow = s.ncand > a.scratch_cap;
     if (!s.nan0) {
         // Elements collected while the running maximum was still low are dropped by the final bound first.
-        float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         if (cfg.need_sum && n_raw > 1024u) {
             // top_p alone: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was not
             // collected belongs to that tail; collected elements can join it from the bottom for as long as the
@@ -673,7 +746,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             const float c2 = cfg.inv_t * 1.4426950408889634f;
             double mine = 0.0;
             for (uint32_t i = tid; i < n_raw; i += kThreads) {
-                const float w = __uint_as_float(scratch[i].x);
+                const float w = __uint_as_float(((i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i]).x);
                 if (w >= thr_final) {
                     const float qa = exp2f((w - m) * c2);
                     atomicAdd(&fh[order_key(w) >> kBinShift], qa);
@@ -714,14 +787,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 if (lane == 0 && budget > 0.0 && cut > 0 && cut < kBins) {
                     const float edge = key_to_float((uint32_t)cut << kBinShift);
                     if (edge == edge)
-                        s.thr_topk_bits = __float_as_uint(fmaxf(__uint_as_float(s.thr_topk_bits), edge));
+                        s.thr_topk_key = max(s.thr_topk_key, (uint32_t)cut << kBinShift);
                 }
             }
             __syncthreads();
-            thr_final = fmaxf(thr_final, __uint_as_float(s.thr_topk_bits));
+            thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = scratch[i];
+            const uint2 c = (i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i];
             if (!(__uint_as_float(c.x) >= thr_final))
                 continue;
             const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
@@ -739,12 +812,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // More candidates than the shared-memory sort holds, and no truncation orders them: the draw walks them
         // in ascending id (sampler.cpp:64-73). The exact weights are laid out by column in scratch and one thread
         // adds and walks them in the reference's order and precision; the other threads stage tiles for it.
-        const float thr_final = fmaxf(keep_threshold(cfg, m), __uint_as_float(s.thr_topk_bits));
+        const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         for (uint32_t i = tid; i < V; i += kThreads)
             qrow[i] = 0.0f;
         __syncthreads();
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = scratch[i];
+            const uint2 c = (i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i];
             if (!(__uint_as_float(c.x) >= thr_final))
                 continue;
             const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
@@ -754,7 +827,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         __threadfence_block();
         __syncthreads();
         float* stage = &s.ring[0][0];
-        const int32_t draft_col = (a.mode == kModeVerify) ? (a.draft[row] - a.id_offset) : -1;
+        const int32_t draft_col = (a.mode == kModeVerify) ? (draft_row - a.id_offset) : -1;
         float total = 0.0f, q_draft = 0.0f;
         // pass 0: float total (and the draft's weight); pass 1: the walk
         float r = 0.0f, walk_total = 0.0f, eps = 0.0f;
@@ -819,7 +892,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 if (tid == 0) {
                     walk_total = total;
                     if (a.mode == kModeVerify) {
-                        acc = __fmul_rn(a.u[row], total) < q_draft;
+                        acc = __fmul_rn(u_row, total) < q_draft;
                         if (acc) {
                             tok = draft_col + a.id_offset;
                             prob = __fdiv_rn(q_draft, total);
@@ -828,7 +901,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                             walk_total = __fsub_rn(total, q_draft);
                         }
                     }
-                    const float uu = (a.mode == kModeVerify) ? a.u2[row] : (a.u ? a.u[row] : 0.0f);
+                    const float uu = (a.mode == kModeVerify) ? u2_row : u_row;
                     r = __fmul_rn(uu, walk_total);
                     eps = 1e-6f * walk_total;
                     s.n_final = 0;
@@ -916,7 +989,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             // weight; elements below the histogram bound were not collected, so the bound itself must map to a
             // strictly smaller weight than the k-th.
             const float qk = q_at(cfg.top_k - 1);
-            const float edge = __uint_as_float(s.thr_topk_bits);
+            const float edge = key_to_float(s.thr_topk_key);
             if (edge > -FLT_MAX) {
                 const float qe = expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t));
                 if (qe >= qk)
@@ -951,7 +1024,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // total and the walk, float, left to right (sampler.cpp:64-73, 80-83)
         float total = 0.0f;
         float q_draft = 0.0f;
-        int32_t draft = (a.mode == kModeVerify) ? a.draft[row] : -1;
+        int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
         for (uint32_t i = 0; i < n; ++i) {
             const float q = q_at(i);
             total = __fadd_rn(total, q);
@@ -969,7 +1042,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             bool skip_draft = false;
             float walk_total = total;
             if (a.mode == kModeVerify) { // sampler.cpp:100-106
-                acc = __fmul_rn(a.u[row], total) < q_draft;
+                acc = __fmul_rn(u_row, total) < q_draft;
                 if (acc) {
                     tok = draft;
                     prob = __fdiv_rn(q_draft, total);
@@ -984,7 +1057,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
             if (tok < 0) {
-                const float uu = (a.mode == kModeVerify) ? a.u2[row] : a.u[row];
+                const float uu = (a.mode == kModeVerify) ? u2_row : u_row;
                 r = __fmul_rn(uu, walk_total);
                 const float eps = 1e-6f * walk_total;
                 int32_t last = -1;
@@ -1026,6 +1099,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         if (a.accepted) a.accepted[row] = acc;
         if (a.total_out) a.total_out[row] = total;
         s.n_final = n;
+        if (a.timing)
+            a.timing[(size_t)row * 64 + 3] = global_ns();
     }
     __syncthreads();
     if (a.cand_ids || a.cand_q) {

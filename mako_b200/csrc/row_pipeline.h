@@ -50,6 +50,8 @@ struct RowKernelArgs {
     // scratch owned by the handle
     uint32_t* scratch;     // [batch][3*scratch_cap] words: raw candidates (logit bits, column), then a float per column
     uint32_t scratch_cap;
+    unsigned long long* timing; // optional [batch][64] ns timestamps: start, set-up done, streaming done, end, set-up steps
+    uint32_t dbg;          // profiling switches (0 in production)
     int mode;
     int use_bulk_copy;     // 1: TMA bulk staging (aligned rows); 0: plain loads
 };
