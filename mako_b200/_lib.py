@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmako_b200.so")
+LIB_PATH = os.environ.get("MAKO_B200_LIB") or os.path.join(HERE, "libmako_b200.so")
 
 MK_OK = 0
 MK_ERR_INVALID_ARGUMENT = 1

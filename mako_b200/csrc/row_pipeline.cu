@@ -28,33 +28,41 @@
 
 #include <cfloat>
 
+#ifndef MK_TILE
+#define MK_TILE 4096
+#endif
+#ifndef MK_STAGES
+#define MK_STAGES 4
+#endif
+
 namespace mk {
 
 namespace {
 
-constexpr int kTile = 4096;   // floats per tile (16 KB)
-constexpr int kStages = 3;
+constexpr int kTile = MK_TILE;   // floats per tile
+constexpr int kStages = MK_STAGES;
 constexpr int kProducerThreads = 32;
 constexpr int kFixers = 64;
 constexpr int kReaders = 256;
 constexpr int kThreads = kProducerThreads + kFixers + kReaders;
 constexpr int kReaderWarps = kReaders / 32;
+constexpr int kVec = kTile / (kReaders * 4); // 128-bit loads per reader thread per tile
+constexpr int kEl = kVec * 4;
+static_assert(kVec * kReaders * 4 == kTile, "a tile is a whole number of 128-bit loads per reader thread");
 constexpr int kHistCap = 4096;  // history entries de-duplicated in shared memory; longer histories scan global memory
 constexpr int kBmWords = 5120;  // history bitmap: one bit per column, vocabularies up to 163840 columns
 constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
-constexpr int kSortCap = 8192;  // 64-bit sort keys: the ring and the history bitmap/prefix behind it (78 KB) hold them
-constexpr int kCandSmem = 2048;
+constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) once the streaming is over
 constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = 21;
-constexpr uint32_t kBarFix = 1, kBarRead = 2;
+constexpr uint32_t kBarRead = 2;
 
 struct __align__(128) Smem {
     float ring[kStages][kTile];     // tile ring; after the streaming, with `table`, the sort area of the finish
     uint32_t bitmap[kBmWords];      // bit c set: column c was generated (long histories: per-tile id counters)
-    uint16_t prefix[kBmWords];      // number of set bits in the words before this one = rank of its first set bit
     uint32_t counts[kHistCap / 2];  // occurrences per distinct generated column, by rank, two 16-bit counters a word
     uint32_t hist[kBins];           // top_k: counts per key bin
-    uint2 cbuf[kCandSmem];          // the first raw candidates (logit bits, column); later ones go to global scratch
+    uint16_t wpre[kBmWords];        // set bits before each bitmap word = rank of its first generated column
     double warp_sum[kThreads / 32];
     uint64_t full[kStages], ready[kStages], empty[kStages];
     unsigned long long best_key;    // (order key of the row maximum << 32) | ~column: first argmax wins
@@ -67,6 +75,7 @@ struct __align__(128) Smem {
     uint32_t hi_group;              // highest non-empty group of 32 histogram bins
     uint32_t n_final;
     uint32_t flags;
+    uint32_t n_distinct;            // distinct generated columns
 };
 
 struct RowCfg {
@@ -175,6 +184,30 @@ __device__ __forceinline__ unsigned long long pack_by_column(float q, uint32_t c
     return ((unsigned long long)col << 32) | __float_as_uint(q);
 }
 
+// Penalties (sampler.cpp:23-28) for the generated columns with ranks [r_lo, r_hi) — the ones whose bitmap words lie
+// in [w_lo, w_hi) — spread evenly over n_thr threads (this one is `thr`): a rank is turned back into its column by a
+// binary search over the per-word ranks and a find-n-th-set-bit in the word, and indexes the count directly. Every
+// column is touched by exactly one thread. `tile` points at column `col0` of the row in shared memory.
+__device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t* wpre, const uint32_t* counts,
+                                         float* tile, uint32_t col0, uint32_t w_lo, uint32_t w_hi, uint32_t r_lo,
+                                         uint32_t r_hi, uint32_t thr, uint32_t n_thr, const RowCfg& cfg)
+{
+    for (uint32_t r = r_lo + thr; r < r_hi; r += n_thr) {
+        uint32_t lo = w_lo, hi = w_hi; // largest word in [lo, hi) whose rank is <= r
+        while (hi - lo > 1u) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if ((uint32_t)wpre[mid] <= r)
+                lo = mid;
+            else
+                hi = mid;
+        }
+        const uint32_t bit = __fns(bitmap[lo], 0u, (int)(r - (uint32_t)wpre[lo]) + 1);
+        const uint32_t n = (counts[r >> 1] >> ((r & 1u) * 16u)) & 0xffffu;
+        const uint32_t loc = (lo << 5) + bit - col0;
+        tile[loc] = penalise(tile[loc], n, cfg);
+    }
+}
+
 // Bitonic sort of n2 (power of two) 64-bit keys in shared memory by the whole CTA.
 __device__ void block_sort(unsigned long long* keys, uint32_t n2)
 {
@@ -246,7 +279,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
-            mbar_init(&s.ready[i], kFixers / 32);
+            mbar_init(&s.ready[i], 1);
             mbar_init(&s.empty[i], kReaderWarps);
         }
         s.best_key = 0ull;
@@ -298,6 +331,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
     }
     if (use_table) {
+        uint16_t* const wpre = s.wpre;
         // The generated tokens as the reference keeps them (a multiset id -> count, sampler.cpp:15-18), in a form
         // the readers can consult per column without searching: a bitmap of generated columns, the number of set
         // bits before each bitmap word (so a column's rank among the distinct ones is one popcount away), and the
@@ -335,9 +369,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             for (uint32_t w = 0; w < warp; ++w)
                 before += wtot[w];
             for (uint32_t w = w0; w < w1; ++w) {
-                s.prefix[w] = (uint16_t)before;
+                wpre[w] = (uint16_t)before;
                 before += __popc(s.bitmap[w]);
             }
+            if (w1 == bm_words && w0 < w1)
+                s.n_distinct = before; // the thread that holds the last word
         }
         __syncthreads();
 #pragma unroll
@@ -346,9 +382,41 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             const int64_t col64 = (j < hlen) ? ((int64_t)hv[hi] - a.id_offset) : -1;
             if (col64 >= 0 && col64 < (int64_t)V) {
                 const uint32_t col = (uint32_t)col64;
-                const uint32_t rank = s.prefix[col >> 5] + __popc(s.bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
+                const uint32_t rank = wpre[col >> 5] + __popc(s.bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
                 atomicAdd(&s.counts[rank >> 1], 1u << ((rank & 1u) * 16u));
             }
+        }
+        __syncthreads();
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 4] = global_ns();
+    }
+    // The tiles that were requested before the set-up have landed by now: all warps apply the sparse edits to them
+    // together (the first tiles hold the most frequent token ids, by far the largest share of the history), then
+    // the fix-up warps carry on alone with the tiles that follow.
+    uint32_t prefixed = 0;
+    if ((use_table || nb > 0) && !long_history && tiles_issued > 0) {
+        prefixed = tiles_issued;
+        bool ok = true;
+        for (uint32_t t = 0; t < prefixed; ++t)
+            ok = mbar_wait(&s.full[t], 0) && ok;
+        if (!ok)
+            atomicExch(&s.abort_flag, 1u);
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 5] = global_ns();
+        const uint32_t span = min(prefixed * (uint32_t)kTile, V);
+        if (nb > 0) {
+            for (uint32_t j = tid; j < nb; j += kThreads) {
+                const mk_bias be = brow[j];
+                const int64_t loc = (int64_t)be.id - a.id_offset;
+                if (be.id >= 0 && loc >= 0 && loc < (int64_t)span)
+                    s.ring[0][loc] = __fadd_rn(s.ring[0][loc], be.value); // stages 0.. are contiguous
+            }
+            __syncthreads();
+        }
+        if (use_table) {
+            const uint32_t w_hi = min((span + 31u) >> 5, bm_words);
+            fix_hits(s.bitmap, s.wpre, s.counts, &s.ring[0][0], 0u, 0u, w_hi, 0u,
+                     (w_hi < bm_words) ? (uint32_t)s.wpre[w_hi] : s.n_distinct, tid, kThreads, cfg);
         }
         __syncthreads();
     }
@@ -381,7 +449,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 break;
             if (a.use_bulk_copy) {
                 if (lane == 0) {
+#ifndef MK_NO_FENCE
                     fence_proxy_async();
+#endif
                     const uint32_t bytes = (n_t * 4u) & ~15u;
                     for (uint32_t e = bytes / 4; e < n_t; ++e)
                         dst[e] = src[e];
@@ -401,62 +471,55 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
         }
     } else if (warp <= kFixers / 32) {
-        // fix-up
+        // fix-up: each of the two warps owns every other tile (a long history: warp 0 owns them all, because its
+        // per-tile counters are shared), so two tiles are edited at a time and nothing synchronises across warps
         if (has_fix) {
-            const uint32_t ft = tid - kProducerThreads;
-            for (uint32_t t = 0; t < n_tiles; ++t) {
+            const uint32_t fw = warp - 1;
+            if (fw == 0 && lane == 0)
+                for (uint32_t t = 0; t < prefixed; ++t) // edited by all warps above
+                    mbar_arrive(&s.ready[t]);
+            const uint32_t t_step = long_history ? 1u : (uint32_t)(kFixers / 32);
+            uint32_t t_first = prefixed;
+            if (!long_history)
+                t_first += (fw + (kFixers / 32) - (prefixed % (kFixers / 32))) % (kFixers / 32); // t % 2 == fw
+            const bool idle = long_history && fw != 0;
+            for (uint32_t t = t_first; t < n_tiles && !idle; t += t_step) {
                 const uint32_t st = t % kStages, k = t / kStages;
                 float* tp = s.ring[st];
                 const uint32_t base = t * kTile;
                 const uint32_t n_t = min((uint32_t)kTile, V - base);
-                // After a timeout the remaining tiles are walked without waiting, so that the named barriers below
-                // stay matched across the fix-up threads.
                 if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 22)))
                     atomicExch(&s.abort_flag, 1u);
                 if (nb > 0) {
-                    for (uint32_t j = ft; j < nb; j += kFixers) {
+                    for (uint32_t j = lane; j < nb; j += 32) {
                         const mk_bias be = brow[j];
                         const int64_t loc = (int64_t)be.id - a.id_offset - (int64_t)base;
                         if (be.id >= 0 && loc >= 0 && loc < (int64_t)n_t)
                             tp[loc] = __fadd_rn(tp[loc], be.value);
                     }
-                    if (has_hist)
-                        named_barrier(kBarFix, kFixers);
+                    __syncwarp();
                 }
                 if (use_table) {
-                    // penalties (sampler.cpp:23-28): the tile's generated columns are the set bits of its bitmap
-                    // words; a column's rank among all generated columns indexes its count. Each column is touched
-                    // by exactly one thread.
-                    const uint32_t w_begin = base >> 5, w_end = min((base + n_t + 31u) >> 5, bm_words);
-                    for (uint32_t wd = w_begin + ft; wd < w_end; wd += kFixers) {
-                        uint32_t bits = s.bitmap[wd];
-                        uint32_t rank = s.prefix[wd];
-                        while (bits) {
-                            const uint32_t bpos = __ffs(bits) - 1;
-                            bits &= bits - 1;
-                            const uint32_t loc = (wd << 5) + bpos - base;
-                            const uint32_t n = (s.counts[rank >> 1] >> ((rank & 1u) * 16u)) & 0xffffu;
-                            ++rank;
-                            tp[loc] = penalise(tp[loc], n, cfg);
-                        }
-                    }
+                    const uint32_t w_lo = base >> 5, w_hi = min((base + n_t + 31u) >> 5, bm_words);
+                    fix_hits(s.bitmap, s.wpre, s.counts, tp, base, w_lo, w_hi, (uint32_t)s.wpre[w_lo],
+                             (w_hi < bm_words) ? (uint32_t)s.wpre[w_hi] : s.n_distinct, lane, 32u, cfg);
                 } else if (has_hist) {
-                    {
-                        for (uint32_t j = ft; j < hlen; j += kFixers) {
-                            const int64_t loc = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
-                            if (loc >= 0 && loc < (int64_t)n_t)
-                                atomicAdd(&cnt[(uint32_t)loc >> 1], 1u << (((uint32_t)loc & 1u) * 16u));
-                        }
-                        named_barrier(kBarFix, kFixers);
-                        for (uint32_t j = ft; j < hlen; j += kFixers) {
-                            const int64_t loc64 = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
-                            if (loc64 >= 0 && loc64 < (int64_t)n_t) {
-                                const uint32_t loc = (uint32_t)loc64, sh = (loc & 1u) * 16u;
-                                const uint32_t old = atomicAnd(&cnt[loc >> 1], ~(0xffffu << sh));
-                                const uint32_t n = (old >> sh) & 0xffffu;
-                                if (n)
-                                    tp[loc] = penalise(tp[loc], n, cfg);
-                            }
+                    // long history: count the tile's ids in 16-bit counters, then the first lane to clear a
+                    // counter owns that id and applies the penalties with its count
+                    for (uint32_t j = lane; j < hlen; j += 32) {
+                        const int64_t loc = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
+                        if (loc >= 0 && loc < (int64_t)n_t)
+                            atomicAdd(&cnt[(uint32_t)loc >> 1], 1u << (((uint32_t)loc & 1u) * 16u));
+                    }
+                    __syncwarp();
+                    for (uint32_t j = lane; j < hlen; j += 32) {
+                        const int64_t loc64 = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
+                        if (loc64 >= 0 && loc64 < (int64_t)n_t) {
+                            const uint32_t loc = (uint32_t)loc64, sh = (loc & 1u) * 16u;
+                            const uint32_t old = atomicAnd(&cnt[loc >> 1], ~(0xffffu << sh));
+                            const uint32_t n = (old >> sh) & 0xffffu;
+                            if (n)
+                                tp[loc] = penalise(tp[loc], n, cfg);
                         }
                     }
                 }
@@ -477,20 +540,23 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         for (uint32_t t = 0; t < n_tiles; ++t) {
             const uint32_t st = t % kStages, k = t / kStages;
             const uint32_t base = t * kTile;
-            uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+            uint32_t mw[kVec];
+#pragma unroll
+            for (int j = 0; j < kVec; ++j)
+                mw[j] = 0xffffffffu;
             if (mrow) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < kVec; ++j) {
                     const uint32_t i0 = base + j * 1024 + rt * 4;
                     mw[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
                 }
             }
             if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 22)))
                 atomicExch(&s.abort_flag, 1u); // keep walking: the named barriers below must stay matched
-            float w[16];
+            float w[kEl];
             const float4* tp4 = reinterpret_cast<const float4*>(s.ring[st]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < kVec; ++j) {
                 const float4 v = tp4[j * 256 + rt];
                 w[4 * j + 0] = v.x;
                 w[4 * j + 1] = v.y;
@@ -503,7 +569,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 
             if (mrow) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < kVec; ++j) {
                     const uint32_t bits = mw[j] >> ((rt * 4) & 31);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
@@ -513,7 +579,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
             if (base + kTile > V) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < kVec; ++j)
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
                         if (base + j * 1024 + rt * 4 + c >= V)
@@ -524,13 +590,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 
             float tm = ninf;
 #pragma unroll
-            for (int e = 0; e < 16; ++e)
+            for (int e = 0; e < kEl; ++e)
                 tm = fmaxf(tm, w[e]);
             const float old_best = best;
             if (tm > best) {
                 best = tm;
 #pragma unroll
-                for (int e = 15; e >= 0; --e)
+                for (int e = kEl - 1; e >= 0; --e)
                     if (w[e] == tm)
                         best_col = (int32_t)(base + (e >> 2) * 1024 + rt * 4 + (e & 3));
             }
@@ -547,7 +613,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     sum_acc *= (double)exp2f((old_best - best) * c2);
                 float p = 0.0f;
 #pragma unroll
-                for (int e = 0; e < 16; ++e)
+                for (int e = 0; e < kEl; ++e)
                     p += exp2f((w[e] - best) * c2);
                 sum_acc += (double)p;
             }
@@ -559,7 +625,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
                 if (tm >= thr) {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e)
+                    for (int e = 0; e < kEl; ++e)
                         if (w[e] >= thr) {
                             const uint32_t bin = order_key(w[e]) >> kBinShift;
                             atomicAdd(&s.hist[bin], 1u);
@@ -593,13 +659,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
             if (collect && tm >= thr) {
 #pragma unroll
-                for (int e = 0; e < 16; ++e)
+                for (int e = 0; e < kEl; ++e)
                     if (w[e] >= thr) {
                         const uint32_t slot = atomicAdd(&s.ncand, 1u);
                         const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-                        if (slot < (uint32_t)kCandSmem)
-                            s.cbuf[slot] = c;
-                        else if (slot < a.scratch_cap)
+                        if (slot < a.scratch_cap)
                             scratch[slot] = c;
                     }
             }
@@ -669,7 +733,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         const uint32_t n_all = min(s.ncand, a.scratch_cap);
         const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         for (uint32_t i = tid; i < n_all; i += kThreads) {
-            const uint2 c = (i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i];
+            const uint2 c = scratch[i];
             if (__uint_as_float(c.x) >= thr_final) {
                 const uint32_t slot = atomicAdd(&s.nsurv, 1u);
                 if (slot < (uint32_t)kSortCap)
@@ -746,7 +810,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             const float c2 = cfg.inv_t * 1.4426950408889634f;
             double mine = 0.0;
             for (uint32_t i = tid; i < n_raw; i += kThreads) {
-                const float w = __uint_as_float(((i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i]).x);
+                const float w = __uint_as_float((scratch[i]).x);
                 if (w >= thr_final) {
                     const float qa = exp2f((w - m) * c2);
                     atomicAdd(&fh[order_key(w) >> kBinShift], qa);
@@ -794,7 +858,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = (i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i];
+            const uint2 c = scratch[i];
             if (!(__uint_as_float(c.x) >= thr_final))
                 continue;
             const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
@@ -817,7 +881,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             qrow[i] = 0.0f;
         __syncthreads();
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = (i < (uint32_t)kCandSmem) ? s.cbuf[i] : scratch[i];
+            const uint2 c = scratch[i];
             if (!(__uint_as_float(c.x) >= thr_final))
                 continue;
             const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
