@@ -82,3 +82,24 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src.lower(), f"{f} mentions the oracle"
+
+
+def test_cpp_header_compiles_and_mirrors_the_reference_errors(tmp_path):
+    """include/mako_b200/sampler.hpp: same constructor signature as the reference class; an empty vocabulary throws
+    std::invalid_argument (src/gen/sampler.cpp:11-12) before any device is touched."""
+    import subprocess
+    src = tmp_path / "t.cpp"
+    src.write_text(
+        '#include <mako_b200/sampler.hpp>\n#include <cstdio>\n'
+        'int main() { using namespace mako_b200::gen; SamplingParams p; p.temperature = 0.7f; p.top_k = 40;\n'
+        '  try { Sampler s(p, 0, 1); } catch (const std::invalid_argument& e) { std::puts(e.what()); return 0; }\n'
+        '  return 1; }\n')
+    exe = tmp_path / "t"
+    lib_dir = os.path.join(ROOT, "mako_b200")
+    subprocess.check_call(["g++", "-std=c++20", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                           "-L", lib_dir, "-lmako_b200", f"-Wl,-rpath,{lib_dir}", "-Wl,--allow-shlib-undefined"])
+    import torch  # its CUDA wheels carry libcudart; expose it to the child
+    cudart = [os.path.join(os.path.dirname(torch.__file__), "..", "nvidia", "cuda_runtime", "lib")]
+    env = dict(os.environ, LD_LIBRARY_PATH=":".join(cudart + [os.environ.get("LD_LIBRARY_PATH", "")]))
+    out = subprocess.run([str(exe)], env=env, capture_output=True, text=True)
+    assert out.returncode == 0 and "empty vocabulary" in out.stdout
