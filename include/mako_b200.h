@@ -112,6 +112,20 @@ int mk_check_sampling(const mk_sampling_params* p);
 int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, const mk_sample_out* out,
                             void* stream);
 
+/* No counterpart in the reference. mk_sampler_sample_batch for callers that must not allocate device memory — code
+ * that runs inside someone else's memory plan (an inference server that hands every byte out at start-up, a plugin
+ * loaded into a process whose allocator it may not touch) or at a point where cudaMalloc is off limits — and so
+ * cannot create an mk_sampler, whose scratch is cudaMalloc'ed. Same inputs, same outputs, same results; the kernel's
+ * candidate scratch is a fixed array inside the library instead (about 15 MiB on each GPU that loads the library,
+ * kept until the process exits). Limits: at most MK_STATIC_MAX_ROWS rows per call and MK_STATIC_MAX_VOCAB columns;
+ * larger arguments return MK_ERR_INVALID_ARGUMENT. The call itself allocates nothing. The first call on a device
+ * also looks up the array's device address; make that first call before any stream capture begins. All calls on a
+ * device share the one array: two calls that overlap on the GPU (different streams, or different host threads)
+ * race on it — run them one after the other. */
+#define MK_STATIC_MAX_ROWS 8u
+#define MK_STATIC_MAX_VOCAB 163840u
+int mk_sample_rows_static(int device, const mk_rows* rows, const float* u, const mk_sample_out* out, void* stream);
+
 /* Replaces Sampler::verify (sampler.cpp:86-107) for rows->batch (sequence, position) rows with deterministic
  * drafts: draft[b] is accepted iff u_accept[b]*total < q(draft); else the draft is removed and a token is drawn
  * with u_redraw[b]. accepted[b] is 0/1, out->token[b] the returned token. */

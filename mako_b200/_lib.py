@@ -98,6 +98,7 @@ def _load() -> C.CDLL:
     lib.mk_sampler_destroy.argtypes = [vp]
     lib.mk_sampler_destroy.restype = None
     lib.mk_sampler_sample_batch.argtypes = [vp, C.POINTER(RowsC), vp, C.POINTER(SampleOutC), vp]
+    lib.mk_sample_rows_static.argtypes = [C.c_int, C.POINTER(RowsC), vp, C.POINTER(SampleOutC), vp]
     lib.mk_sampler_verify_batch.argtypes = [vp, C.POINTER(RowsC), vp, vp, vp, C.POINTER(SampleOutC), vp, vp]
     lib.mk_sampler_verify_pq_batch.argtypes = [vp, C.POINTER(RowsC), vp, C.c_uint64, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.mk_spec_resolve.argtypes = [vp, C.c_uint32, C.c_uint32, vp, vp, vp, vp, vp]

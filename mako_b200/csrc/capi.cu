@@ -280,6 +280,54 @@ int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, 
     return MK_OK;
 }
 
+// ---- sampling without any allocation --------------------------------------------------------------------------------
+// The row kernel parks its raw candidate list in global memory. For callers that cannot allocate, that list lives
+// in this file-scope device array instead of a handle's buffer: MK_STATIC_MAX_ROWS rows of 12 bytes per column
+// for vocabularies up to MK_STATIC_MAX_VOCAB, about 15 MiB on every GPU that loads the library, held until the
+// process exits. The symbol is a host-side stand-in here; the address the kernel needs is asked for once per device.
+static __device__ __align__(256) uint32_t g_static_scratch[(size_t)MK_STATIC_MAX_ROWS * 3u * MK_STATIC_MAX_VOCAB];
+static uint32_t* g_static_scratch_ptr[64] = {};
+
+int mk_sample_rows_static(int device, const mk_rows* rows, const float* u, const mk_sample_out* out, void* stream)
+{
+    if (device < 0 || device >= 64)
+        return fail(MK_ERR_INVALID_ARGUMENT, "device %d out of range", device);
+    if (!rows)
+        return fail(MK_ERR_INVALID_ARGUMENT, "null rows");
+    if (rows->batch > MK_STATIC_MAX_ROWS)
+        return fail(MK_ERR_INVALID_ARGUMENT, "batch %u above the static limit of %u rows", rows->batch,
+                    (unsigned)MK_STATIC_MAX_ROWS);
+    if (rows->n_vocab > MK_STATIC_MAX_VOCAB)
+        return fail(MK_ERR_INVALID_ARGUMENT, "n_vocab %u above the static limit of %u columns", rows->n_vocab,
+                    (unsigned)MK_STATIC_MAX_VOCAB);
+    mk_sampler tmp; // a view for the shared argument checks; owns nothing
+    tmp.device = device;
+    tmp.n_vocab = MK_STATIC_MAX_VOCAB;
+    tmp.max_batch = MK_STATIC_MAX_ROWS;
+    if (int rc = check_rows(&tmp, rows))
+        return rc;
+    if (!out || !out->token)
+        return fail(MK_ERR_INVALID_ARGUMENT, "out->token is required");
+    if (!u && !all_greedy(rows))
+        return fail(MK_ERR_INVALID_ARGUMENT, "uniforms are required unless every row is greedy");
+    DeviceGuard g(device);
+    if (!g.ok)
+        return fail(MK_ERR_CUDA, "cannot select device %d", device);
+    if (!g_static_scratch_ptr[device]) { // first call on this device: resolve the symbol with the device current
+        void* p = nullptr;
+        MK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_scratch_ptr[device] = static_cast<uint32_t*>(p);
+    }
+    tmp.scratch = g_static_scratch_ptr[device];
+    mk::RowKernelArgs a;
+    fill_common(a, &tmp, rows);
+    fill_out(a, out);
+    a.u = u;
+    a.mode = mk::kModeSample;
+    MK_CUDA(mk::launch_row_kernel(a, rows->batch, (cudaStream_t)stream));
+    return MK_OK;
+}
+
 int mk_sampler_verify_batch(mk_sampler* s, const mk_rows* rows, const int32_t* draft, const float* u_accept,
                             const float* u_redraw, const mk_sample_out* out, int32_t* accepted, void* stream)
 {
