@@ -3,13 +3,18 @@
 // What it replaces: mako::gen::Sampler::distribution / draw / sample / verify (src/gen/sampler.cpp:20-107), which
 // the reference runs on the host, one row at a time, over a copy of the logits.
 //
-// Shape of the kernel (352 threads = 11 warps, ~92 KB shared memory, two CTAs per SM):
+// Shape of the kernel (352 threads = 11 warps, ~110 KB shared memory, two CTAs per SM):
 //   warp 0        producer: streams the row through a 4-stage ring of 16 KB tiles with untiled bulk asynchronous
-//                 copies (TMA, cp.async.bulk, no multicast), completion on an mbarrier per stage.
-//   warps 1-2     fix-up: once a tile has landed, apply the sparse edits in shared memory — logit bias, then the
-//                 repetition / presence / frequency penalties of the token history, each distinct id once with its
-//                 count (sampler.cpp:23-28). The history is bucketed by tile in shared memory at kernel start;
-//                 counts come from a 16-bit histogram of the tile's ids.
+//                 copies (TMA, cp.async.bulk, no multicast), completion on an mbarrier per stage; the first tiles are
+//                 requested before the set-up so that they fly meanwhile.
+//   set-up        all warps: the token history becomes a bitmap of generated columns, the rank of each bitmap
+//                 word's first set bit (prefix popcount) and, by rank, the count of each generated column — the
+//                 multiset the reference keeps in an unordered_map (sampler.cpp:15-18). The penalties of the tiles
+//                 that have landed by then (the dense head of the history) are applied by all warps, spread evenly
+//                 by rank (binary search over the word ranks + find-n-th-set-bit).
+//   warps 1-2     fix-up: each owns every other tile; once it has landed, apply the sparse edits in shared memory —
+//                 logit bias, then the repetition / presence / frequency penalties of the tile's generated columns,
+//                 each once with its count (sampler.cpp:23-28) — and release it to the readers.
 //   warps 3-10    readers: 128-bit shared loads, allowed-token mask, running row maximum (warp shuffles), and
 //                 collection of every element that can still become a candidate: the keep thresholds of min_p,
 //                 top_k and top_p are all lower-bounded by a function of the running maximum (or of a histogram of
