@@ -40,7 +40,7 @@ int cuda_fail(cudaError_t e, const char* what)
 // 12*cap-byte block starts on a 16-byte boundary (the raw candidates are read and written as 8-byte pairs).
 inline uint32_t scratch_cap(uint32_t n_vocab) { return (n_vocab + 3u) & ~3u; }
 
-constexpr uint32_t kPqCap = 1024;      // candidates per list in p/q verification
+constexpr uint32_t kPqCap = 4096;      // candidates per list in p/q verification
 constexpr uint32_t kMaxTiles = 512, kTile = 4096;
 
 } // namespace
