@@ -194,6 +194,7 @@ def main() -> None:
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 4])
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (default: min(steps, 20))")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--streams", type=int, default=2, help="batches in flight (sampler handles and streams)")
     ap.add_argument("--no-graph", action="store_true", help="launch each step from the host instead of a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -232,11 +233,15 @@ def main() -> None:
         if "bias_ids" in d:
             g["kw"]["bias"] = torch.from_numpy(pack_bias(d["bias_ids"], d["bias_vals"])).to(dev)
         dev_sets.append(g)
-    sampler = BatchSampler(v, b, local_rank)
+    # args.streams sampler handles (scratch and outputs of their own), step k on handle and stream k % streams: two
+    # batches in flight, as a server that double-buffers its decode steps has them, so that one launch's set-up and
+    # finish overlap the other's streaming instead of leaving the memory system idle.
+    samplers = [BatchSampler(v, b, local_rank) for _ in range(max(1, args.streams))]
+    sampler = samplers[0]
 
     def step(k):
         g = dev_sets[k % N_SETS]
-        return sampler.sample(g["logits"], params, g["u"], **g["kw"])
+        return samplers[k % len(samplers)].sample(g["logits"], params, g["u"], **g["kw"])
 
     def barrier():
         torch.cuda.synchronize()
@@ -250,17 +255,24 @@ def main() -> None:
     # The timed loop replays a CUDA graph of one cycle over the input sets, so that the host's launch path (Python,
     # ctypes) is not what is measured; --no-graph launches step by step instead.
     graph = None
-    cycles = max(1, args.steps // N_SETS)
+    per_graph = N_SETS * 4   # steps captured in one graph
+    cycles = max(1, args.steps // per_graph)
     if not args.no_graph:
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                for k in range(N_SETS):
-                    step(k)
+                subs = [torch.cuda.Stream(device=dev) for _ in samplers]
+                for sub in subs:
+                    sub.wait_stream(side)
+                for k in range(per_graph):
+                    with torch.cuda.stream(subs[k % len(subs)]):
+                        step(k)
+                for sub in subs:
+                    side.wait_stream(sub)
         torch.cuda.current_stream(dev).wait_stream(side)
-        args.steps = cycles * N_SETS
+        args.steps = cycles * per_graph
         graph.replay()
     barrier()
     clocks = ClockSampler(local_rank) if rank == 0 else None
@@ -275,8 +287,9 @@ def main() -> None:
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    flags = sampler.flags[:b].cpu().numpy()
-    tokens_dev = sampler.token[:b].cpu().numpy().copy()
+    last = samplers[(args.steps - 1) % len(samplers)]
+    flags = last.flags[:b].cpu().numpy()
+    tokens_dev = last.token[:b].cpu().numpy().copy()
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -325,7 +338,7 @@ def main() -> None:
             "config": {"workload": workload_name(cfg), "batch_per_gpu": b, "n_vocab": v,
                        "n_history": cfg["n_history"], "parallelism": f"row-sharded x{world}, no collective",
                        "l2": f"{N_SETS} distinct input sets cycled ({N_SETS * rb * b / 1e6:.0f} MB > L2)",
-                       "seed": SEED, "launch": "host loop" if graph is None else f"CUDA graph of {N_SETS} steps replayed"},
+                       "seed": SEED, "launch": "host loop" if graph is None else f"CUDA graph of {per_graph} steps replayed, {len(samplers)} batches in flight"},
             "effective_gbs": value * rb / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": committed_traffic(f"config{args.config}"),

@@ -36,35 +36,28 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
+// One potentially blocking probe of the barrier phase: the hardware parks the thread until the phase completes or
+// the suspend-time hint (nanoseconds) runs out, so a waiting warp does not compete for issue slots by spinning.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-#ifdef MK_SPIN
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
         : "memory");
     return ok != 0;
 }
 
-// Bounded wait: gives up after `limit` polls (each poll itself blocks for a hardware-defined short time) and
-// reports false, so that a lost copy or a logic error ends the kernel with a status instead of hanging the GPU.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22))
+// Bounded wait: gives up after `limit` probes and reports false, so that a lost copy or a logic error ends the
+// kernel with a status instead of hanging the GPU. (2^17 probes of up to 20 us each: a few seconds at most.)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 17))
 {
-    for (uint32_t i = 0; i < limit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity))
             return true;
-#ifndef MK_SPIN
-        if (i > 64)
-            __nanosleep(32);
-#endif
-    }
     return false;
 }
 

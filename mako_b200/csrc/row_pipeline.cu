@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 float* tp = s.ring[st];
                 const uint32_t base = t * kTile;
                 const uint32_t n_t = min((uint32_t)kTile, V - base);
-                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 22)))
+                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
                     atomicExch(&s.abort_flag, 1u);
                 if (nb > 0) {
                     for (uint32_t j = lane; j < nb; j += 32) {
@@ -556,7 +556,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     mw[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
                 }
             }
-            if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 22)))
+            if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
                 atomicExch(&s.abort_flag, 1u); // keep walking: the named barriers below must stay matched
             float w[kEl];
             const float4* tp4 = reinterpret_cast<const float4*>(s.ring[st]);
