@@ -18,8 +18,7 @@ __device__ __constant__ unsigned long long kExp2Tab[32] = {
 #include "exp2_table.inc"
 };
 
-// `tab` = a copy of kExp2Tab the caller keeps close (shared memory), or kExp2Tab itself.
-__device__ __forceinline__ float expf_host_exact(float x, const unsigned long long* tab = kExp2Tab)
+__device__ __forceinline__ float expf_host_exact(float x)
 {
     if (!(x >= -0x1.9fe368p6f)) {       // below log(2^-150), -inf, or NaN
         return (x != x) ? x : 0.0f;
@@ -37,7 +36,7 @@ __device__ __forceinline__ float expf_host_exact(float x, const unsigned long lo
     const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
     kd = __dsub_rn(kd, shift);
     const double r = __fma_rn(inv_ln2_n, xd, -kd);
-    const unsigned long long t = tab[ki & 31ull] + (ki << 47);
+    const unsigned long long t = kExp2Tab[ki & 31ull] + (ki << 47);
     const double s = __longlong_as_double((long long)t);
     const double zz = __fma_rn(c0, r, c1);
     const double r2 = __dmul_rn(r, r);

@@ -69,7 +69,6 @@ struct __align__(128) Smem {
     uint32_t hist[kBins];           // top_k: counts per key bin
     uint16_t wpre[kBmWords];        // set bits before each bitmap word = rank of its first generated column
     double warp_sum[kThreads / 32];
-    unsigned long long exp2tab[32]; // the exponential's table, fetched once per CTA during the set-up
     uint64_t full[kStages], ready[kStages], empty[kStages];
     unsigned long long best_key;    // (order key of the row maximum << 32) | ~column: first argmax wins
     uint32_t m_key;                 // running maximum, as order key
@@ -97,7 +96,7 @@ struct RowCfg {
 __device__ __forceinline__ unsigned long long global_ns()
 {
     unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)::"memory");
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
 
@@ -259,10 +258,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const uint32_t nb = a.bias ? a.n_bias : 0u;
     const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
     const bool has_fix = nb > 0 || has_hist; // work for the fix-up warps
-    // The first raw candidates stay in shared memory — in the top_k histogram's space, when neither that histogram
-    // nor the mass histogram of the finish needs it; the rest go to the row's scratch in global memory.
-    uint2* const cb = reinterpret_cast<uint2*>(s.hist);
-    const uint32_t cb_n = (cfg.hist_mode || cfg.need_sum) ? 0u : (uint32_t)(kBins / 2);
     const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
     // Per-row scratch: scratch_cap raw candidates (logit bits, column), then scratch_cap floats indexed by column
     // that the large-list path uses.
@@ -283,8 +278,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             hv[i] = (j < hlen) ? __ldg(hrow + j) : 0;
         }
     }
-    if (tid < 32)
-        s.exp2tab[tid] = kExp2Tab[tid];
     // ---- set-up -------------------------------------------------------------------------------------------------
     if (a.timing && tid == 0)
         a.timing[(size_t)row * 64 + 0] = global_ns();
@@ -675,9 +668,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     if (w[e] >= thr) {
                         const uint32_t slot = atomicAdd(&s.ncand, 1u);
                         const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-                        if (slot < cb_n)
-                            cb[slot] = c;
-                        else if (slot < a.scratch_cap)
+                        if (slot < a.scratch_cap)
                             scratch[slot] = c;
                     }
             }
@@ -705,8 +696,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         return;
     }
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 14] = global_ns();
     const bool any_finite = s.best_key != 0ull;
     float m = any_finite ? key_to_float((uint32_t)(s.best_key >> 32)) : -__int_as_float(0x7f800000);
     uint32_t arg_col = any_finite ? (0xffffffffu - (uint32_t)(s.best_key & 0xffffffffull)) : 0u;
@@ -718,8 +707,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (mrow && !any_finite && !s.nan0)
         flags |= MK_FLAG_ALL_MASKED;
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 15] = global_ns();
     // exact row total for need_sum: sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
     double total_approx = 0.0;
     if (cfg.need_sum) {
@@ -751,7 +738,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         const uint32_t n_all = min(s.ncand, a.scratch_cap);
         const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         for (uint32_t i = tid; i < n_all; i += kThreads) {
-            const uint2 c = (i < cb_n) ? cb[i] : scratch[i];
+            const uint2 c = scratch[i];
             if (__uint_as_float(c.x) >= thr_final) {
                 const uint32_t slot = atomicAdd(&s.nsurv, 1u);
                 if (slot < (uint32_t)kSortCap)
@@ -807,8 +794,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         return;
     }
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 9] = global_ns();
     // exact weights of the collected elements, min_p filter (sampler.cpp:33-35)
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
     const uint32_t n_raw = min(s.ncand, a.scratch_cap);
@@ -877,14 +862,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             __syncthreads();
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
-        if (a.timing && tid == 0)
-            a.timing[(size_t)row * 64 + 13] = global_ns();
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = (i < cb_n) ? cb[i] : scratch[i];
+            const uint2 c = scratch[i];
             if (!(__uint_as_float(c.x) >= thr_final))
                 continue;
             const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
-            const float q = expf_host_exact(x, s.exp2tab);
+            const float q = expf_host_exact(x);
             if (q >= cfg.minp_eff && q > 0.0f) {
                 const uint32_t slot = atomicAdd(&s.nsurv, 1u);
                 if (slot < (uint32_t)kSortCap)
@@ -893,8 +876,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
     }
     __syncthreads();
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 11] = global_ns();
     uint32_t n = s.nsurv;
     if (!overflow && n > (uint32_t)kSortCap && !cfg.use_topp && !(cfg.top_k > 0 && cfg.top_k < n)) {
         // More candidates than the shared-memory sort holds, and no truncation orders them: the draw walks them
@@ -905,10 +886,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             qrow[i] = 0.0f;
         __syncthreads();
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = (i < cb_n) ? cb[i] : scratch[i];
+            const uint2 c = scratch[i];
             if (!(__uint_as_float(c.x) >= thr_final))
                 continue;
-            const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t), s.exp2tab);
+            const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
             if (q >= cfg.minp_eff && q > 0.0f)
                 qrow[c.y] = q;
         }
@@ -1046,45 +1027,23 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     const bool cut_k = cfg.top_k > 0 && cfg.top_k < n;       // sampler.cpp:39
     const bool sorted = cut_k || cfg.use_topp;               // else ascending id
-    if (n <= 32u) {
-        // the usual case, a handful of candidates: one warp ranks them with shuffles, no block-wide barrier
-        if (warp == 0) {
-            unsigned long long key = ~0ull;
-            if (lane < n) {
-                const unsigned long long raw = keys[lane];
-                const float q = __uint_as_float((uint32_t)(raw >> 32));
-                const uint32_t col = (uint32_t)(raw & 0xffffffffull);
-                key = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
-            }
-            uint32_t pos = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                pos += (__shfl_sync(0xffffffffu, key, j) < key) ? 1u : 0u; // keys are distinct (they hold the column)
-            __syncwarp();
-            if (lane < n)
-                keys[pos] = key;
-            __syncwarp();
+    uint32_t n2 = 2;
+    while (n2 < n)
+        n2 <<= 1;
+    for (uint32_t i = tid; i < n2; i += kThreads) {
+        unsigned long long key = ~0ull;
+        if (i < n) {
+            const unsigned long long raw = keys[i];
+            const float q = __uint_as_float((uint32_t)(raw >> 32));
+            const uint32_t col = (uint32_t)(raw & 0xffffffffull);
+            key = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
         }
-    } else {
-        uint32_t n2 = 2;
-        while (n2 < n)
-            n2 <<= 1;
-        for (uint32_t i = tid; i < n2; i += kThreads) {
-            unsigned long long key = ~0ull;
-            if (i < n) {
-                const unsigned long long raw = keys[i];
-                const float q = __uint_as_float((uint32_t)(raw >> 32));
-                const uint32_t col = (uint32_t)(raw & 0xffffffffull);
-                key = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
-            }
-            keys[i] = key;
-        }
-        __syncthreads();
-        block_sort(keys, n2);
+        keys[i] = key;
     }
+    __syncthreads();
+    if (n > 1)
+        block_sort(keys, n2);
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 12] = global_ns();
     if (tid == 0) {
         auto q_at = [&](uint32_t i) -> float {
             const unsigned long long key = keys[i];
@@ -1101,7 +1060,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             const float qk = q_at(cfg.top_k - 1);
             const float edge = key_to_float(s.thr_topk_key);
             if (edge > -FLT_MAX) {
-                const float qe = expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t), s.exp2tab);
+                const float qe = expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t));
                 if (qe >= qk)
                     flags |= MK_FLAG_GUARD_BAND;
             }
