@@ -82,7 +82,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+                 "-lms", "50"], stdout=self.tmp, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -188,7 +188,7 @@ def workload_name(cfg) -> str:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=8192)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 4])
@@ -287,6 +287,29 @@ def main() -> None:
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
+    # the same K steps with one batch in flight (plain back-to-back launches on one stream), for the record
+    ms_serial = None
+    if graph is not None and len(samplers) > 1:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1, stream=side):
+                for k in range(per_graph):
+                    samplers[0].sample(dev_sets[k % N_SETS]["logits"], params, dev_sets[k % N_SETS]["u"],
+                                       **dev_sets[k % N_SETS]["kw"])
+        torch.cuda.current_stream(dev).wait_stream(side)
+        g1.replay()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(cycles):
+            g1.replay()
+        s1.record()
+        barrier()
+        ms_serial = s0.elapsed_time(s1)
+        graph.replay()          # leave the outputs of the headline mode in place for the parity check below
+        barrier()
     last = samplers[(args.steps - 1) % len(samplers)]
     flags = last.flags[:b].cpu().numpy()
     tokens_dev = last.token[:b].cpu().numpy().copy()
@@ -347,6 +370,9 @@ def main() -> None:
             "e2e": {"value": world * b * e2e_steps / e2e_sec, "unit": "rows/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 12 * b, "steps": e2e_steps},
             "gpu_launches": args.steps,
+            "one_batch_in_flight": None if ms_serial is None else {
+                "ms_per_step": ms_serial / args.steps, "value": b * args.steps / (ms_serial / 1e3),
+                "roofline_frac": rb * b / (ms_serial / args.steps / 1e3) / 1e9 / peak},
             "clocks": clk,
             "parity": {"rows_flagged_near_cdf_boundary": int((flags & 1).sum()),
                        "rows_flagged_guard_band": int(((flags & 2) != 0).sum()),
