@@ -33,13 +33,12 @@ typedef enum mk_status {
 
 /* Per-row result flags (bit set). */
 #define MK_FLAG_NEAR_CDF_BOUNDARY 0x001u /* u*total within 1e-6*total of a CDF boundary beside the chosen token */
-#define MK_FLAG_GUARD_BAND        0x002u /* a keep/drop decision fell inside the numeric guard band (see DESIGN) */
+#define MK_FLAG_GUARD_BAND        0x002u /* a keep/drop decision fell inside the numeric guard band */
 #define MK_FLAG_NO_CANDIDATE      0x004u /* nothing finite survived: first argmax returned (sampler.cpp:37-38) */
 #define MK_FLAG_ALL_MASKED        0x008u /* the mask allowed no token of this row */
 #define MK_FLAG_OVERFLOW          0x010u /* more candidates than the handle's capacity: token = -1 */
 #define MK_FLAG_VP_TRUNCATED      0x020u /* vocab-parallel: the nucleus may reach past a shard's top-k list */
 #define MK_FLAG_TIMEOUT           0x040u /* a bounded device-side wait ran out: token = -1 */
-#define MK_FLAG_SECOND_PASS       0x080u /* the row was streamed a second time to settle a guard-band decision */
 
 /* Field for field mako::gen::SamplingParams (src/gen/sampler.hpp:12-20). temperature <= 0 selects greedy. */
 typedef struct mk_sampling_params {
@@ -116,7 +115,7 @@ int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, 
  * that runs inside someone else's memory plan (an inference server that hands every byte out at start-up, a plugin
  * loaded into a process whose allocator it may not touch) or at a point where cudaMalloc is off limits — and so
  * cannot create an mk_sampler, whose scratch is cudaMalloc'ed. Same inputs, same outputs, same results; the kernel's
- * candidate scratch is a fixed array inside the library instead (about 15 MiB on each GPU that loads the library,
+ * candidate scratch is a fixed array inside the library instead (about 20 MiB on each GPU that loads the library,
  * kept until the process exits). Limits: at most MK_STATIC_MAX_ROWS rows per call and MK_STATIC_MAX_VOCAB columns;
  * larger arguments return MK_ERR_INVALID_ARGUMENT. The call itself allocates nothing. The first call on a device
  * also looks up the array's device address; make that first call before any stream capture begins. All calls on a

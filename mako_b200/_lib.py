@@ -24,7 +24,6 @@ FLAG_ALL_MASKED = 0x008
 FLAG_OVERFLOW = 0x010
 FLAG_VP_TRUNCATED = 0x020
 FLAG_TIMEOUT = 0x040
-FLAG_SECOND_PASS = 0x080
 
 
 class SamplingParamsC(C.Structure):

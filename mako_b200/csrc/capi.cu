@@ -37,7 +37,7 @@ int cuda_fail(cudaError_t e, const char* what)
     } while (0)
 
 // Entries of raw-candidate scratch per row: the vocabulary rounded up to a multiple of 4, so that every row's
-// 12*cap-byte block starts on a 16-byte boundary (the raw candidates are read and written as 8-byte pairs).
+// 16*cap-byte block starts on a 16-byte boundary (the raw candidates are read and written as 8-byte pairs).
 inline uint32_t scratch_cap(uint32_t n_vocab) { return (n_vocab + 3u) & ~3u; }
 
 constexpr uint32_t kPqCap = 4096;      // candidates per list in p/q verification
@@ -48,7 +48,7 @@ constexpr uint32_t kMaxTiles = 512, kTile = 4096;
 struct mk_sampler {
     int device = 0;
     uint32_t n_vocab = 0, max_batch = 0;
-    uint32_t* scratch = nullptr; // [max_batch][3*n_vocab] words: raw candidates (a row can never overflow it) + a float per column
+    uint32_t* scratch = nullptr; // [max_batch][4*n_vocab] words: raw candidates (a row can never overflow it) + sort buffer / a float per column
     // p/q verification lists
     int32_t *p_ids = nullptr, *q_ids = nullptr;
     float *p_q = nullptr, *q_q = nullptr, *p_total = nullptr, *q_total = nullptr, *q_prob = nullptr;
@@ -224,7 +224,7 @@ int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t m
         if (e == cudaSuccess)
             e = cudaMalloc(p, bytes);
     };
-    alloc((void**)&s->scratch, b * (size_t)scratch_cap(n_vocab) * 12);
+    alloc((void**)&s->scratch, b * (size_t)scratch_cap(n_vocab) * 16);
     alloc((void**)&s->p_ids, b * kPqCap * 4);
     alloc((void**)&s->q_ids, b * kPqCap * 4);
     alloc((void**)&s->p_q, b * kPqCap * 4);
@@ -282,10 +282,10 @@ int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, 
 
 // ---- sampling without any allocation --------------------------------------------------------------------------------
 // The row kernel parks its raw candidate list in global memory. For callers that cannot allocate, that list lives
-// in this file-scope device array instead of a handle's buffer: MK_STATIC_MAX_ROWS rows of 12 bytes per column
-// for vocabularies up to MK_STATIC_MAX_VOCAB, about 15 MiB on every GPU that loads the library, held until the
+// in this file-scope device array instead of a handle's buffer: MK_STATIC_MAX_ROWS rows of 16 bytes per column
+// for vocabularies up to MK_STATIC_MAX_VOCAB, about 20 MiB on every GPU that loads the library, held until the
 // process exits. The symbol is a host-side stand-in here; the address the kernel needs is asked for once per device.
-static __device__ __align__(256) uint32_t g_static_scratch[(size_t)MK_STATIC_MAX_ROWS * 3u * MK_STATIC_MAX_VOCAB];
+static __device__ __align__(256) uint32_t g_static_scratch[(size_t)MK_STATIC_MAX_ROWS * 4u * MK_STATIC_MAX_VOCAB];
 static uint32_t* g_static_scratch_ptr[64] = {};
 
 int mk_sample_rows_static(int device, const mk_rows* rows, const float* u, const mk_sample_out* out, void* stream)

@@ -234,6 +234,63 @@ __device__ void block_sort(unsigned long long* keys, uint32_t n2)
     }
 }
 
+// One pass of a merge sort over n 64-bit keys in global memory: runs of w sorted keys in `src` are merged pairwise
+// into `dst`. Every key finds its place by a binary search in the partner run — the lower bound for a key of the left
+// run, the upper bound for one of the right run, so equal keys would still land in distinct slots. Four searches
+// per thread are interleaved to overlap their memory latencies.
+__device__ void merge_pass(const unsigned long long* src, unsigned long long* dst,
+                           uint32_t n, uint32_t w)
+{
+    for (uint32_t i0 = threadIdx.x * 4u; i0 < n; i0 += kThreads * 4u) {
+        unsigned long long key[4];
+        uint32_t lo[4], hi[4], own[4], base[4];
+        bool right[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = i0 + (uint32_t)k;
+            lo[k] = hi[k] = own[k] = base[k] = 0;
+            right[k] = false;
+            key[k] = 0;
+            if (i < n) {
+                key[k] = src[i];
+                const uint32_t pair = i / (2u * w), in_pair = i - pair * 2u * w;
+                const uint32_t l0 = pair * 2u * w, l1 = min(l0 + w, n), r1 = min(l0 + 2u * w, n);
+                const bool left = in_pair < w;
+                right[k] = !left;
+                own[k] = left ? (i - l0) : (i - l1);
+                base[k] = l0;
+                lo[k] = left ? l1 : l0;      // partner run [lo, hi)
+                hi[k] = left ? r1 : l1;
+            }
+        }
+        uint32_t a[4], b[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            a[k] = lo[k];
+            b[k] = hi[k];
+        }
+        bool busy = true;
+        while (busy) { // four searches in step
+            busy = false;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (a[k] < b[k]) {
+                    const uint32_t mid = (a[k] + b[k]) >> 1;
+                    const unsigned long long v = src[mid];
+                    if (v < key[k] || (right[k] && v == key[k]))
+                        a[k] = mid + 1;
+                    else
+                        b[k] = mid;
+                    busy = true;
+                }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (i0 + (uint32_t)k < n)
+                dst[base[k] + own[k] + (a[k] - lo[k])] = key[k];
+    }
+}
+
 } // namespace
 
 __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKernelArgs a)
@@ -259,10 +316,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
     const bool has_fix = nb > 0 || has_hist; // work for the fix-up warps
     const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
-    // Per-row scratch: scratch_cap raw candidates (logit bits, column), then scratch_cap floats indexed by column
-    // that the large-list path uses.
-    uint2* __restrict__ scratch = reinterpret_cast<uint2*>(a.scratch + (size_t)row * 3u * a.scratch_cap);
-    float* __restrict__ qrow = reinterpret_cast<float*>(a.scratch + (size_t)row * 3u * a.scratch_cap + 2u * a.scratch_cap);
+    // Per-row scratch, 16 bytes per column: scratch_cap raw candidates (logit bits, column) — sorted in place as
+    // 64-bit keys by the large sorted-list path — then as much again: the merge sort's second buffer, or (large
+    // unsorted lists) one float per column.
+    uint2* __restrict__ scratch = reinterpret_cast<uint2*>(a.scratch + (size_t)row * 4u * a.scratch_cap);
+    float* __restrict__ qrow = reinterpret_cast<float*>(a.scratch + (size_t)row * 4u * a.scratch_cap + 2u * a.scratch_cap);
 
     const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
     const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
@@ -430,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         a.timing[(size_t)row * 64 + 1] = global_ns();
     float best = -__int_as_float(0x7f800000);
     int32_t best_col = -1;
-    double sum_acc = 0.0; // sum of exp2((l - best) * c2) over this thread's elements (need_sum)
+    double sum_acc = 0.0; // need_sum: sum of exp2((l - best) * c2) over this thread's uncollected elements
 
     if (warp == 0) {
         // producer
@@ -541,6 +599,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         const float c2 = cfg.inv_t * 1.4426950408889634f;
         const float ninf = -__int_as_float(0x7f800000);
         const bool collect = !cfg.greedy || a.mode == kModeVpLocal;
+        const bool sum_all = a.mode == kModeVpLocal;
         float warp_pub = ninf;
         for (uint32_t t = 0; t < n_tiles; ++t) {
             const uint32_t st = t % kStages, k = t / kStages;
@@ -613,17 +672,18 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         atomicMax(&s.m_key, order_key(wm));
                 }
             }
+            float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
             if (cfg.need_sum && best > ninf) {
+                // Approximate weight of what is NOT collected below (a shard record sums everything): the collected
+                // elements get exact weights in the finish, so only the far tail carries the approximation.
                 if (best > old_best)
                     sum_acc *= (double)exp2f((old_best - best) * c2);
                 float p = 0.0f;
 #pragma unroll
                 for (int e = 0; e < kEl; ++e)
-                    p += exp2f((w[e] - best) * c2);
+                    p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
                 sum_acc += (double)p;
             }
-
-            float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
             if (cfg.hist_mode) {
                 // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
                 // where the count from the top reaches k bounds the k-th largest from below.
@@ -707,7 +767,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (mrow && !any_finite && !s.nan0)
         flags |= MK_FLAG_ALL_MASKED;
 
-    // exact row total for need_sum: sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
+    // need_sum: weight of the uncollected tail (the whole row for a shard record), relative to the row maximum:
+    // sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
     double total_approx = 0.0;
     if (cfg.need_sum) {
         double part = 0.0;
@@ -730,6 +791,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         __syncthreads();
         for (int i = 0; i < kThreads / 32; ++i)
             total_approx += s.warp_sum[i];
+        __syncthreads(); // warp_sum is written again below
     }
 
     if (a.mode == kModeVpLocal) {
@@ -798,6 +860,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
     const uint32_t n_raw = min(s.ncand, a.scratch_cap);
     bool overflow = s.ncand > a.scratch_cap;
+    double total_need = 0.0, band_need = 0.0; // need_sum: the row total that top_p scales, and its margin
     if (!s.nan0) {
         // Elements collected while the running maximum was still low are dropped by the final bound first.
         float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
@@ -810,28 +873,35 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             for (uint32_t i = tid; i < kBins; i += kThreads)
                 fh[i] = 0.0f;
             if (tid == 0)
-                s.warp_sum[0] = 0.0;
+                s.warp_sum[0] = s.warp_sum[1] = 0.0;
             __syncthreads();
             const float c2 = cfg.inv_t * 1.4426950408889634f;
-            double mine = 0.0;
+            double mine = 0.0, low = 0.0;
             for (uint32_t i = tid; i < n_raw; i += kThreads) {
                 const float w = __uint_as_float((scratch[i]).x);
+                const float qa = exp2f((w - m) * c2);
                 if (w >= thr_final) {
-                    const float qa = exp2f((w - m) * c2);
                     atomicAdd(&fh[order_key(w) >> kBinShift], qa);
                     mine += (double)qa;
+                } else {
+                    low += (double)qa;
                 }
             }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
+            for (int o = 16; o > 0; o >>= 1) {
                 mine += __shfl_xor_sync(0xffffffffu, mine, o);
-            if (lane == 0)
+                low += __shfl_xor_sync(0xffffffffu, low, o);
+            }
+            if (lane == 0) {
                 atomicAdd(&s.warp_sum[0], mine);
+                atomicAdd(&s.warp_sum[1], low);
+            }
             __syncthreads();
             if (warp == 0) {
                 const double collected = s.warp_sum[0];
-                const double budget = (1.0 - (double)cfg.top_p) * total_approx * 0.999 -
-                                      (fmax(total_approx - collected, 0.0) + 1e-5 * total_approx);
+                const double outside = total_approx + s.warp_sum[1]; // never collected, or below the final bound
+                const double total_est = collected + outside;
+                const double budget = (1.0 - (double)cfg.top_p) * total_est * 0.999 - (outside + 1e-5 * total_est);
                 double cum = 0.0;
                 int cut = 0; // elements in bins below `cut` may be dropped
                 bool stop = false;
@@ -862,21 +932,47 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             __syncthreads();
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
+        double exact = 0.0;
         for (uint32_t i = tid; i < n_raw; i += kThreads) {
             const uint2 c = scratch[i];
-            if (!(__uint_as_float(c.x) >= thr_final))
+            const bool in = __uint_as_float(c.x) >= thr_final;
+            if (!in && !cfg.need_sum)
                 continue;
             const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
             const float q = expf_host_exact(x);
-            if (q >= cfg.minp_eff && q > 0.0f) {
+            if (q == q)
+                exact += (double)q;
+            if (in && q >= cfg.minp_eff && q > 0.0f) {
                 const uint32_t slot = atomicAdd(&s.nsurv, 1u);
                 if (slot < (uint32_t)kSortCap)
                     keys[slot] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
             }
         }
+        if (cfg.need_sum) {
+            // top_p's total (sampler.cpp:45-47) covers every column: exact weights for all that was collected, the
+            // approximate sum for the rest. The margin that goes with it is 1e-5 of the approximate part plus the
+            // rounding of a double sum taken in another order than the reference's.
+            __syncthreads();
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                exact += __shfl_xor_sync(0xffffffffu, exact, o);
+            if (lane == 0)
+                s.warp_sum[warp] = exact;
+            __syncthreads();
+            double sum = 0.0;
+            for (int i = 0; i < kThreads / 32; ++i)
+                sum += s.warp_sum[i];
+            total_need = sum + total_approx;
+            band_need = 1e-5 * total_approx + 0x1p-40 * total_need;
+        }
     }
     __syncthreads();
     uint32_t n = s.nsurv;
+    if (a.timing && tid == 0) {
+        a.timing[(size_t)row * 64 + 9] = n_raw;
+        a.timing[(size_t)row * 64 + 10] = n;
+        a.timing[(size_t)row * 64 + 11] = global_ns();
+    }
     if (!overflow && n > (uint32_t)kSortCap && !cfg.use_topp && !(cfg.top_k > 0 && cfg.top_k < n)) {
         // More candidates than the shared-memory sort holds, and no truncation orders them: the draw walks them
         // in ascending id (sampler.cpp:64-73). The exact weights are laid out by column in scratch and one thread
@@ -1002,6 +1098,189 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             if (a.n_cand) a.n_cand[row] = n;
             if (a.accepted) a.accepted[row] = acc;
             if (a.total_out) a.total_out[row] = total;
+            if (a.timing) a.timing[(size_t)row * 64 + 3] = global_ns();
+        }
+        return;
+    }
+    if (!overflow && n > (uint32_t)kSortCap && a.mode != kModeDistOnly) {
+        // More candidates than the shared-memory sort holds, and a truncation that orders them (the unordered case
+        // returned above): a flat row under top_p, or a very large top_k. The candidates are sorted in global
+        // memory — 8192-key runs in shared memory, then merge passes between the two halves of the row's scratch —
+        // and one thread walks the sorted list through shared-memory tiles, in the reference's order and precision.
+        unsigned long long* KA = reinterpret_cast<unsigned long long*>(scratch) + a.scratch_cap; // second half
+        unsigned long long* KB = reinterpret_cast<unsigned long long*>(scratch);                 // over the raw list
+        const float thr2 = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
+        if (tid == 0)
+            s.nsurv = 0;
+        __syncthreads();
+        for (uint32_t i = tid; i < n_raw; i += kThreads) { // survivors, compacted, as sort keys
+            const uint2 c = scratch[i];
+            if (__uint_as_float(c.x) >= thr2) {
+                const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
+                if (q >= cfg.minp_eff && q > 0.0f)
+                    KA[atomicAdd(&s.nsurv, 1u)] = pack_by_weight(q, c.y);
+            }
+        }
+        __syncthreads();
+        for (uint32_t r0 = 0; r0 < n; r0 += (uint32_t)kSortCap) {
+            for (uint32_t i = tid; i < (uint32_t)kSortCap; i += kThreads)
+                keys[i] = (r0 + i < n) ? KA[r0 + i] : ~0ull;
+            __syncthreads();
+            block_sort(keys, (uint32_t)kSortCap);
+            for (uint32_t i = tid; i < (uint32_t)kSortCap; i += kThreads)
+                if (r0 + i < n)
+                    KA[r0 + i] = keys[i];
+            __syncthreads();
+        }
+        const unsigned long long* P = KA;
+        {
+            unsigned long long *src = KA, *dst = KB;
+            for (uint32_t w = (uint32_t)kSortCap; w < n; w <<= 1) {
+                merge_pass(src, dst, n, w);
+                __syncthreads();
+                unsigned long long* t = src;
+                src = dst;
+                dst = t;
+            }
+            P = src;
+        }
+        const bool cut_k2 = cfg.top_k > 0 && cfg.top_k < n;
+        uint32_t n_list = cut_k2 ? cfg.top_k : n;
+        if (cut_k2 && tid == 0) {
+            // weights equal to the k-th may exist below the histogram bound, where nothing was collected
+            const float qk = __uint_as_float(~(uint32_t)(P[cfg.top_k - 1] >> 32));
+            const float edge = key_to_float(s.thr_topk_key);
+            if (edge > -FLT_MAX && expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t)) >= qk)
+                flags |= MK_FLAG_GUARD_BAND;
+        }
+        // thread 0 walks `count` keys in order, a 4096-key tile at a time; body returns true to stop
+        auto staged_walk = [&](uint32_t count, auto&& body) {
+            for (uint32_t t0 = 0; t0 < count; t0 += 4096u) {
+                const uint32_t nt = min(4096u, count - t0);
+                for (uint32_t e = tid; e < nt; e += kThreads)
+                    keys[e] = P[t0 + e];
+                __syncthreads();
+                if (tid == 0) {
+                    bool stop = false;
+                    for (uint32_t e = 0; e < nt && !stop; ++e)
+                        stop = body(keys[e], t0 + e);
+                    s.hi_group = stop ? 1u : 0u;
+                }
+                __syncthreads();
+                if (s.hi_group)
+                    break;
+            }
+        };
+        const int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
+        double want = 0.0, band = 0.0;
+        if (cfg.use_topp) { // sampler.cpp:44-61
+            double total = 0.0;
+            if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
+                total = total_need;
+                band = band_need;
+            } else {
+                double part = 0.0;
+                for (uint32_t i = tid; i < n_list; i += kThreads)
+                    part += (double)__uint_as_float(~(uint32_t)(P[i] >> 32));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+                    part += __shfl_xor_sync(0xffffffffu, part, o);
+                if (lane == 0)
+                    s.warp_sum[warp] = part;
+                __syncthreads();
+                for (int i = 0; i < kThreads / 32; ++i)
+                    total += s.warp_sum[i];
+                band = 0x1p-30 * total; // the block-wide sum is not the reference's left-to-right one
+            }
+            want = (double)cfg.top_p * total;
+        }
+        // walk 1: nucleus length, float total, the draft's weight
+        double run = 0.0, prev = 0.0;
+        float total_f = 0.0f, q_draft = 0.0f;
+        uint32_t n_nuc = 0;
+        staged_walk(n_list, [&](unsigned long long key, uint32_t) -> bool {
+            if (cfg.use_topp && !(run < want))
+                return true;
+            const float q = __uint_as_float(~(uint32_t)(key >> 32));
+            prev = run;
+            run += (double)q;
+            total_f = __fadd_rn(total_f, q);
+            if ((int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset == draft)
+                q_draft = q;
+            ++n_nuc;
+            return false;
+        });
+        // walk 2: the draw
+        int32_t tok = -1, acc = 0, last = -1;
+        float prob = 0.0f, last_q = 0.0f, r = 0.0f, walk_total = 0.0f, eps = 0.0f;
+        bool skip_draft = false, first = true;
+        uint32_t picked = 0xffffffffu;
+        if (tid == 0) {
+            if (cfg.use_topp) {
+                if (cfg.need_sum && run < want)
+                    flags |= MK_FLAG_GUARD_BAND;
+                if (n_nuc >= 1 && (fabs(run - want) <= band || (n_nuc >= 2 && fabs(prev - want) <= band)))
+                    flags |= MK_FLAG_GUARD_BAND;
+            }
+            n_nuc = max(n_nuc, 1u);
+            walk_total = total_f;
+            if (a.mode == kModeVerify) {
+                acc = __fmul_rn(u_row, total_f) < q_draft;
+                if (acc) {
+                    tok = draft;
+                    prob = __fdiv_rn(q_draft, total_f);
+                } else {
+                    skip_draft = true;
+                    walk_total = __fsub_rn(total_f, q_draft);
+                }
+            }
+            r = __fmul_rn((a.mode == kModeVerify) ? u2_row : u_row, walk_total);
+            eps = 1e-6f * walk_total;
+            s.n_final = n_nuc;
+            s.nsurv = acc ? 1u : 0u;
+        }
+        __syncthreads();
+        const uint32_t n_fin = s.n_final;
+        if (!s.nsurv)
+            staged_walk(n_fin, [&](unsigned long long key, uint32_t idx) -> bool {
+                const int32_t id = (int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset;
+                if (skip_draft && id == draft)
+                    return false;
+                const float q = __uint_as_float(~(uint32_t)(key >> 32));
+                last = id;
+                last_q = q;
+                if (r < q) {
+                    tok = id;
+                    prob = __fdiv_rn(q, walk_total);
+                    picked = idx;
+                    if ((!first && r < eps) || (idx + 1 < n_fin && __fsub_rn(q, r) < eps))
+                        flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                    return true;
+                }
+                r = __fsub_rn(r, q);
+                first = false;
+                return false;
+            });
+        if (tid == 0) {
+            if (tok < 0) { // rounding: the last candidate (sampler.cpp:72)
+                tok = last;
+                prob = __fdiv_rn(last_q, walk_total);
+            }
+            if (a.token) a.token[row] = tok;
+            if (a.prob) a.prob[row] = prob;
+            if (a.flags) a.flags[row] = flags;
+            if (a.n_cand) a.n_cand[row] = n_fin;
+            if (a.accepted) a.accepted[row] = acc;
+            if (a.total_out) a.total_out[row] = total_f;
+            if (a.timing) a.timing[(size_t)row * 64 + 3] = global_ns();
+        }
+        if (a.cand_ids || a.cand_q) {
+            const uint32_t nf = min(n_fin, a.cand_cap);
+            for (uint32_t i = tid; i < nf; i += kThreads) {
+                const unsigned long long key = P[i];
+                if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset;
+                if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + i] = __uint_as_float(~(uint32_t)(key >> 32));
+            }
         }
         return;
     }
@@ -1070,8 +1349,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             double total = 0.0;
             double band;
             if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
-                total = total_approx;
-                band = 1e-5 * total;
+                total = total_need;
+                band = band_need;
             } else {
                 for (uint32_t i = 0; i < n; ++i)
                     total += (double)q_at(i);

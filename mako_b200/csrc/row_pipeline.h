@@ -48,7 +48,7 @@ struct RowKernelArgs {
     void* vp_records;
     uint32_t vp_k;
     // scratch owned by the handle
-    uint32_t* scratch;     // [batch][3*scratch_cap] words: raw candidates (logit bits, column), then a float per column
+    uint32_t* scratch;     // [batch][4*scratch_cap] words: raw candidates (logit bits, column), then a sort buffer / a float per column
     uint32_t scratch_cap;
     unsigned long long* timing; // optional [batch][64] ns timestamps: start, set-up done, streaming done, end, set-up steps
     uint32_t dbg;          // profiling switches (0 in production)

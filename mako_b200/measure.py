@@ -120,6 +120,11 @@ def main():
     p = SamplingParams(temperature=0.8, top_p=0.9, repetition_penalty=1.1, presence_penalty=0.5, frequency_penalty=0.3)
     us = _time(lambda k: s.sample(sets[k % 2]["logits"], p, sets[k % 2]["u"], **sets[k % 2]["kw"]), max(args.steps // 4, 20))
     report("4 1024 x 151552 one launch (row-sharded, N=1)", us, b, b * lib.mk_row_bytes(v, h, 0, 0, 1))
+    fl = s.flags[:b].cpu().numpy()
+    nc = s.n_cand[:b].cpu().numpy()
+    print(json.dumps(dict(config="4 row flags", overflow=int(((fl & 0x10) != 0).sum()),
+                          guard_band=int(((fl & 0x2) != 0).sum()), near_boundary=int((fl & 1).sum()),
+                          nucleus_median=int(np.median(nc)), nucleus_max=int(nc.max()))), flush=True)
     vs = v // n_sh
     rb = lib.mk_vp_record_bytes(k_sh)
     gathered = torch.zeros((n_sh, b, rb), dtype=torch.uint8, device="cuda")

@@ -132,3 +132,35 @@ def test_host_buffer_entry_point(gpu_sampler_factory, ref):
     want = oracle_sample_rows(ref, p, inp)
     assert tok.tolist() == [w["token"] for w in want]
     assert np.allclose(prob, [w["prob"] for w in want], rtol=1e-5)
+
+
+@pytest.mark.parametrize("params", [
+    SamplingParams(temperature=1.0, top_p=0.9),                         # top_p alone: the total covers every column
+    SamplingParams(temperature=1.3, top_p=0.95, min_p=1e-6),            # tens of thousands pass min_p
+    SamplingParams(temperature=1.0, top_k=30000, top_p=0.8),            # a very large top_k, then top_p
+    SamplingParams(temperature=1.0, top_k=20000),                       # top_k alone, longer than the on-chip sort
+], ids=["topp", "minp_topp", "topk_topp", "topk"])
+def test_flat_rows_keep_long_sorted_lists(gpu_sampler_factory, ref, params):
+    """Near-flat rows keep more candidates than the on-chip sort holds; the list is sorted in device memory and
+    must still be the reference's, element for element (sampler.cpp:39-61), for the draw and for verify."""
+    import torch
+    v, b, cap = 60013, 6, 60016
+    rng = np.random.default_rng(17)
+    rows = rng.normal(0, 0.4, size=(b, v)).astype(np.float32)
+    rows[1] = np.round(rows[1] * 8) / 8          # many exact ties in weight: order by id inside a tie
+    rows[2, 1234] = 9.0                          # one spike over a flat floor
+    rows[3] = 0.25                               # all equal
+    u = synth.uniforms(23, b)
+    u2 = synth.uniforms(23, b, purpose=1)
+    res = gpu_rows(gpu_sampler_factory, rows, params, u, cap=cap)
+    want = [ref.sample(params, rows[i], u[i], cap=cap) for i in range(b)]
+    assert max(w["n_cand"] for w in want) > 8192
+    compare_sample(res, want, cap=cap)
+    draft = np.array([w["cand_ids"][min(i, w["n_cand"] - 1)] for i, w in enumerate(want)], dtype=np.int32)
+    s = gpu_sampler_factory(v, b, cap)
+    vr = s.verify(torch.from_numpy(rows).cuda(), params, torch.from_numpy(draft).cuda(), torch.from_numpy(u).cuda(),
+                  torch.from_numpy(u2).cuda())
+    torch.cuda.synchronize()
+    tok, acc = vr.token.cpu().numpy(), vr.accepted.cpu().numpy()
+    for i in range(b):
+        assert (tok[i], bool(acc[i])) == ref.verify(params, rows[i], int(draft[i]), u[i], u2[i]), f"row {i}"
