@@ -60,7 +60,6 @@ constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
 constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) once the streaming is over
 constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = 21;
-constexpr uint32_t kBarRead = 2;
 
 struct __align__(128) Smem {
     float ring[kStages][kTile];     // tile ring; after the streaming, with `table`, the sort area of the finish
@@ -211,6 +210,39 @@ __device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t*
         const uint32_t loc = (lo << 5) + bit - col0;
         tile[loc] = penalise(tile[loc], n, cfg);
     }
+}
+
+// Exclusive prefix of the per-word popcounts of s.bitmap[0, bm_words) into s.wpre, total into s.n_distinct: a set
+// bit's rank among all set bits is then wpre[word] + popcount of the lower bits of its word. Whole CTA; the caller
+// synchronises before (bitmap complete) and after (wpre complete). Each thread takes a contiguous run of words.
+__device__ __forceinline__ void word_ranks(Smem& s, uint32_t bm_words)
+{
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t per = (bm_words + kThreads - 1) / kThreads;
+    const uint32_t w0 = min(tid * per, bm_words), w1 = min(w0 + per, bm_words);
+    uint32_t mine = 0;
+    for (uint32_t w = w0; w < w1; ++w)
+        mine += __popc(s.bitmap[w]);
+    uint32_t inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+        if ((int)lane >= o)
+            inc += y;
+    }
+    uint32_t* wtot = reinterpret_cast<uint32_t*>(s.warp_sum); // 16 words of scratch
+    if (lane == 31)
+        wtot[warp] = inc;
+    __syncthreads();
+    uint32_t before = inc - mine;
+    for (uint32_t w = 0; w < warp; ++w)
+        before += wtot[w];
+    for (uint32_t w = w0; w < w1; ++w) {
+        s.wpre[w] = (uint16_t)before;
+        before += __popc(s.bitmap[w]);
+    }
+    if (w1 == bm_words && w0 < w1)
+        s.n_distinct = before; // the thread that holds the last word
 }
 
 // Bitonic sort of n2 (power of two) 64-bit keys in shared memory by the whole CTA.
@@ -410,34 +442,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
         }
         __syncthreads();
-        {
-            // exclusive prefix of the per-word popcounts: each thread takes a contiguous run of words
-            const uint32_t per = (bm_words + kThreads - 1) / kThreads;
-            const uint32_t w0 = min(tid * per, bm_words), w1 = min(w0 + per, bm_words);
-            uint32_t mine = 0;
-            for (uint32_t w = w0; w < w1; ++w)
-                mine += __popc(s.bitmap[w]);
-            uint32_t inc = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
-                if ((int)lane >= o)
-                    inc += y;
-            }
-            uint32_t* wtot = reinterpret_cast<uint32_t*>(s.warp_sum); // 16 words of scratch
-            if (lane == 31)
-                wtot[warp] = inc;
-            __syncthreads();
-            uint32_t before = inc - mine;
-            for (uint32_t w = 0; w < warp; ++w)
-                before += wtot[w];
-            for (uint32_t w = w0; w < w1; ++w) {
-                wpre[w] = (uint16_t)before;
-                before += __popc(s.bitmap[w]);
-            }
-            if (w1 == bm_words && w0 < w1)
-                s.n_distinct = before; // the thread that holds the last word
-        }
+        word_ranks(s, bm_words);
         __syncthreads();
 #pragma unroll
         for (int hi = 0; hi < kHistPerThread; ++hi) {
@@ -697,12 +702,15 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                             atomicMax(&s.hi_group, bin >> 5);
                         }
                 }
-                named_barrier(kBarRead, kReaders);
-                if (rwarp == 0) {
+                // One reader warp per tile rescans the histogram and raises the bound; nobody waits for it. Counts
+                // only grow and every count is an element at or above its bin's edge, so a bound read from a
+                // histogram that other warps are still adding to has its k elements all the same.
+                __syncwarp();
+                if (rwarp == (t % (kReaders / 32))) {
                     uint32_t cum = 0;
                     int found = -1;
                     for (int g = (int)*(volatile uint32_t*)&s.hi_group; g >= 0 && found < 0; --g) {
-                        const uint32_t cbin = s.hist[g * 32 + lane];
+                        const uint32_t cbin = ((volatile uint32_t*)s.hist)[g * 32 + lane];
                         uint32_t suf = cbin; // suffix sum over lanes >= lane
 #pragma unroll
                         for (int o = 1; o < 32; o <<= 1) {
@@ -717,9 +725,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     }
                     // the lowest key of a bin is its smallest float; bin 0 (NaN keys) is never a bound
                     if (lane == 0 && found > 0)
-                        s.thr_topk_key = max(s.thr_topk_key, (uint32_t)found << kBinShift);
+                        atomicMax(&s.thr_topk_key, (uint32_t)found << kBinShift);
                 }
-                named_barrier(kBarRead, kReaders);
                 thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
             }
             if (collect && tm >= thr) {
@@ -877,14 +884,23 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             __syncthreads();
             const float c2 = cfg.inv_t * 1.4426950408889634f;
             double mine = 0.0, low = 0.0;
-            for (uint32_t i = tid; i < n_raw; i += kThreads) {
-                const float w = __uint_as_float((scratch[i]).x);
-                const float qa = exp2f((w - m) * c2);
-                if (w >= thr_final) {
-                    atomicAdd(&fh[order_key(w) >> kBinShift], qa);
-                    mine += (double)qa;
-                } else {
-                    low += (double)qa;
+            for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
+                float wv[4]; // four loads in flight
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t i = i0 + (uint32_t)k * kThreads;
+                    wv[k] = (i < n_raw) ? __uint_as_float(scratch[i].x) : -__int_as_float(0x7f800000);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float w = wv[k];
+                    const float qa = exp2f((w - m) * c2); // 0 for the filler
+                    if (w >= thr_final) {
+                        atomicAdd(&fh[order_key(w) >> kBinShift], qa);
+                        mine += (double)qa;
+                    } else {
+                        low += (double)qa;
+                    }
                 }
             }
 #pragma unroll
@@ -933,19 +949,28 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
         double exact = 0.0;
-        for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = scratch[i];
-            const bool in = __uint_as_float(c.x) >= thr_final;
-            if (!in && !cfg.need_sum)
-                continue;
-            const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
-            const float q = expf_host_exact(x);
-            if (q == q)
-                exact += (double)q;
-            if (in && q >= cfg.minp_eff && q > 0.0f) {
-                const uint32_t slot = atomicAdd(&s.nsurv, 1u);
-                if (slot < (uint32_t)kSortCap)
-                    keys[slot] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
+        for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
+            uint2 cv[4]; // four loads in flight
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t i = i0 + (uint32_t)k * kThreads;
+                cv[k] = (i < n_raw) ? scratch[i] : make_uint2(0xff800000u, 0u); // filler: -inf
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint2 c = cv[k];
+                const bool in = __uint_as_float(c.x) >= thr_final;
+                if (!in && (!cfg.need_sum || i0 + (uint32_t)k * kThreads >= n_raw))
+                    continue;
+                const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
+                const float q = expf_host_exact(x);
+                if (q == q)
+                    exact += (double)q;
+                if (in && q >= cfg.minp_eff && q > 0.0f) {
+                    const uint32_t slot = atomicAdd(&s.nsurv, 1u);
+                    if (slot < (uint32_t)kSortCap)
+                        keys[slot] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
+                }
             }
         }
         if (cfg.need_sum) {
@@ -1306,62 +1331,190 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     const bool cut_k = cfg.top_k > 0 && cfg.top_k < n;       // sampler.cpp:39
     const bool sorted = cut_k || cfg.use_topp;               // else ascending id
-    uint32_t n2 = 2;
-    while (n2 < n)
-        n2 <<= 1;
-    for (uint32_t i = tid; i < n2; i += kThreads) {
-        unsigned long long key = ~0ull;
-        if (i < n) {
-            const unsigned long long raw = keys[i];
-            const float q = __uint_as_float((uint32_t)(raw >> 32));
-            const uint32_t col = (uint32_t)(raw & 0xffffffffull);
-            key = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
+    // Ascending id needs no sort: a bitmap of the candidates' columns ranks them, and `ord` lists the candidates'
+    // slots by rank. (Vocabularies beyond the bitmap, and lists too short to be worth it, sort by column.)
+    const bool by_rank = !sorted && V <= kMaxBitmapVocab && n > 64u;
+    static_assert(offsetof(Smem, hist) == offsetof(Smem, counts) + sizeof(Smem::counts), "ord spans counts and hist");
+    static_assert(sizeof(Smem::counts) + sizeof(Smem::hist) >= kSortCap * sizeof(uint16_t), "ord holds kSortCap slots");
+    uint16_t* const ord = reinterpret_cast<uint16_t*>(s.counts);
+    if (by_rank) {
+        const uint32_t words = (V + 31u) >> 5;
+        for (uint32_t w = tid; w < words; w += kThreads)
+            s.bitmap[w] = 0u;
+        __syncthreads();
+        for (uint32_t i = tid; i < n; i += kThreads) {
+            const uint32_t col = (uint32_t)(keys[i] & 0xffffffffull);
+            atomicOr(&s.bitmap[col >> 5], 1u << (col & 31u));
         }
-        keys[i] = key;
-    }
-    __syncthreads();
-    if (n > 1)
-        block_sort(keys, n2);
-
-    if (tid == 0) {
-        auto q_at = [&](uint32_t i) -> float {
-            const unsigned long long key = keys[i];
-            return sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
-        };
-        auto col_at = [&](uint32_t i) -> uint32_t {
-            const unsigned long long key = keys[i];
-            return sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
-        };
-        if (cut_k) {
-            // sampler.cpp:40-42. Ties in q with the k-th weight are ordered by id among ALL elements with that
-            // weight; elements below the histogram bound were not collected, so the bound itself must map to a
-            // strictly smaller weight than the k-th.
-            const float qk = q_at(cfg.top_k - 1);
-            const float edge = key_to_float(s.thr_topk_key);
-            if (edge > -FLT_MAX) {
-                const float qe = expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t));
-                if (qe >= qk)
-                    flags |= MK_FLAG_GUARD_BAND;
+        __syncthreads();
+        word_ranks(s, words);
+        __syncthreads();
+        for (uint32_t i = tid; i < n; i += kThreads) {
+            const uint32_t col = (uint32_t)(keys[i] & 0xffffffffull);
+            ord[s.wpre[col >> 5] + __popc(s.bitmap[col >> 5] & ((1u << (col & 31u)) - 1u))] = (uint16_t)i;
+        }
+        __syncthreads();
+    } else {
+        uint32_t n2 = 2;
+        while (n2 < n)
+            n2 <<= 1;
+        for (uint32_t i = tid; i < n2; i += kThreads) {
+            unsigned long long key = ~0ull;
+            if (i < n) {
+                const unsigned long long raw = keys[i];
+                const float q = __uint_as_float((uint32_t)(raw >> 32));
+                const uint32_t col = (uint32_t)(raw & 0xffffffffull);
+                key = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
             }
-            n = cfg.top_k;
+            keys[i] = key;
         }
-        if (cfg.use_topp) { // sampler.cpp:44-61
-            double total = 0.0;
-            double band;
+        __syncthreads();
+        if (n > 1)
+            block_sort(keys, n2);
+    }
+    // the r-th candidate of the list in the reference's order
+    auto fetch = [&](uint32_t r, float& q, uint32_t& col) {
+        if (sorted) {
+            const unsigned long long key = keys[r];
+            q = __uint_as_float(~(uint32_t)(key >> 32));
+            col = (uint32_t)(key & 0xffffffffull);
+        } else if (by_rank) {
+            const unsigned long long key = keys[ord[r]];
+            q = __uint_as_float((uint32_t)(key >> 32));
+            col = (uint32_t)(key & 0xffffffffull);
+        } else {
+            const unsigned long long key = keys[r];
+            q = __uint_as_float((uint32_t)(key & 0xffffffffull));
+            col = (uint32_t)(key >> 32);
+        }
+    };
+    auto q_of = [&](uint32_t r) -> float {
+        float q;
+        uint32_t col;
+        fetch(r, q, col);
+        return q;
+    };
+
+    if (cut_k) {
+        // sampler.cpp:40-42. Ties in q with the k-th weight are ordered by id among ALL elements with that weight;
+        // elements below the histogram bound were not collected, so the bound itself must map to a strictly
+        // smaller weight than the k-th.
+        const float qk = q_of(cfg.top_k - 1);
+        const float edge = key_to_float(s.thr_topk_key);
+        if (edge > -FLT_MAX && expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t)) >= qk)
+            flags |= MK_FLAG_GUARD_BAND;
+        n = cfg.top_k;
+    }
+    const bool short_list = n <= 128u; // one warp does it all, in the reference's own order, without CTA barriers
+    if (cfg.use_topp && !short_list) {
+        // sampler.cpp:44-61: the shortest prefix of the sorted list whose double sum reaches top_p * total. The sums
+        // are taken by the whole CTA (each thread a contiguous run of the list, then a scan over threads); their
+        // rounding differs from the reference's left-to-right sum by far less than the margin inside which a
+        // decision is reported.
+        const uint32_t per = (n + kThreads - 1) / kThreads;
+        const uint32_t r0 = min(tid * per, n), r1 = min(r0 + per, n);
+        double mine = 0.0;
+        for (uint32_t r = r0; r < r1; ++r)
+            mine += (double)q_of(r);
+        double inc = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double y = __shfl_up_sync(0xffffffffu, inc, o);
+            if ((int)lane >= o)
+                inc += y;
+        }
+        __syncthreads(); // warp_sum may still be read
+        if (lane == 31)
+            s.warp_sum[warp] = inc;
+        if (tid == 0)
+            s.n_final = n;
+        __syncthreads();
+        double before = inc - mine, list_total = 0.0;
+        for (uint32_t w = 0; w < (uint32_t)(kThreads / 32); ++w) {
+            if (w < warp)
+                before += s.warp_sum[w];
+            list_total += s.warp_sum[w];
+        }
+        double total, band;
+        if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
+            total = total_need;
+            band = band_need + 0x1p-36 * total;
+        } else {
+            total = list_total;
+            band = 0x1p-36 * total;
+        }
+        const double want = (double)cfg.top_p * total;
+        {
+            double run = before;
+            for (uint32_t r = r0; r < r1; ++r) {
+                run += (double)q_of(r);
+                if (!(run < want)) {
+                    atomicMin(&s.n_final, r + 1u);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        const uint32_t k = s.n_final; // candidates taken: the first count whose sum is not below `want`, else all
+        __syncthreads();
+        {
+            double run = before;
+            for (uint32_t r = r0; r < r1; ++r) {
+                const double prev = run;
+                run += (double)q_of(r);
+                if (r + 1u == k) {
+                    s.warp_sum[0] = run;
+                    s.warp_sum[1] = prev;
+                }
+            }
+        }
+        __syncthreads();
+        const double run = s.warp_sum[0], prev = s.warp_sum[1];
+        if (cfg.need_sum && run < want)
+            flags |= MK_FLAG_GUARD_BAND; // the collected list ended before the nucleus did
+        if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
+            flags |= MK_FLAG_GUARD_BAND;
+        n = max(k, 1u);
+    }
+
+    // Float total and the walk, left to right in the reference's order and precision (sampler.cpp:64-73, 80-83,
+    // 100-106), by one warp: every lane loads one candidate, the values go round by shuffle and every lane runs
+    // the same sequential chain, so the chain never waits for memory.
+    if (warp == 0) {
+        const uint32_t full = 0xffffffffu;
+        const int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
+        if (cfg.use_topp && short_list) { // sampler.cpp:44-61, sequentially
+            double total_d = 0.0, band;
             if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
-                total = total_need;
+                total_d = total_need;
                 band = band_need;
             } else {
-                for (uint32_t i = 0; i < n; ++i)
-                    total += (double)q_at(i);
-                band = 0x1p-40 * total;
+                for (uint32_t base = 0; base < n; base += 32u) {
+                    const float q = (base + lane < n) ? q_of(base + lane) : 0.0f;
+                    const int cnt = (int)min(32u, n - base);
+#pragma unroll 4
+                    for (int j = 0; j < cnt; ++j)
+                        total_d += (double)__shfl_sync(full, q, j);
+                }
+                band = 0x1p-40 * total_d;
             }
-            const double want = (double)cfg.top_p * total;
+            const double want = (double)cfg.top_p * total_d;
             double run = 0.0, prev = 0.0;
             uint32_t k = 0;
-            while (k < n && run < want) {
-                prev = run;
-                run += (double)q_at(k++);
+            bool open = true;
+            for (uint32_t base = 0; base < n && open; base += 32u) {
+                const float q = (base + lane < n) ? q_of(base + lane) : 0.0f;
+                const int cnt = (int)min(32u, n - base);
+#pragma unroll 4
+                for (int j = 0; j < cnt; ++j) {
+                    const double qj = (double)__shfl_sync(full, q, j);
+                    open = open && run < want;
+                    if (open) {
+                        prev = run;
+                        run += qj;
+                        k = base + (uint32_t)j + 1u;
+                    }
+                }
             }
             if (cfg.need_sum && run < want)
                 flags |= MK_FLAG_GUARD_BAND; // the collected list ended before the nucleus did
@@ -1369,25 +1522,33 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 flags |= MK_FLAG_GUARD_BAND;
             n = max(k, 1u);
         }
-        // total and the walk, float, left to right (sampler.cpp:64-73, 80-83)
-        float total = 0.0f;
-        float q_draft = 0.0f;
-        int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
-        for (uint32_t i = 0; i < n; ++i) {
-            const float q = q_at(i);
-            total = __fadd_rn(total, q);
-            if (a.mode == kModeVerify && (int32_t)col_at(i) + a.id_offset == draft)
-                q_draft = q;
+        float total = 0.0f, q_draft = 0.0f;
+        uint32_t draft_idx = 0xffffffffu;
+        for (uint32_t base = 0; base < n; base += 32u) {
+            float q = 0.0f;
+            uint32_t col = 0xffffffffu;
+            if (base + lane < n)
+                fetch(base + lane, q, col);
+            const uint32_t dm = __ballot_sync(full, draft >= 0 && base + lane < n && (int32_t)col + a.id_offset == draft);
+            if (dm) {
+                q_draft = __shfl_sync(full, q, __ffs(dm) - 1);
+                draft_idx = base + (uint32_t)__ffs(dm) - 1u;
+            }
+            const int cnt = (int)min(32u, n - base);
+#pragma unroll 8
+            for (int j = 0; j < cnt; ++j)
+                total = __fadd_rn(total, __shfl_sync(full, q, j));
         }
-        int32_t tok = -1;
+        int32_t tok = -1, acc = 0;
         float prob = 0.0f;
-        int32_t acc = 0;
         if (a.mode == kModeDistOnly) {
-            tok = (int32_t)col_at(0) + a.id_offset;
-            prob = __fdiv_rn(q_at(0), total);
+            float q0;
+            uint32_t c0;
+            fetch(0, q0, c0);
+            tok = (int32_t)c0 + a.id_offset;
+            prob = __fdiv_rn(q0, total);
         } else {
-            float r;
-            bool skip_draft = false;
+            uint32_t skip_idx = 0xffffffffu;
             float walk_total = total;
             if (a.mode == kModeVerify) { // sampler.cpp:100-106
                 acc = __fmul_rn(u_row, total) < q_draft;
@@ -1395,68 +1556,74 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     tok = draft;
                     prob = __fdiv_rn(q_draft, total);
                 } else {
-                    skip_draft = true;
+                    skip_idx = draft_idx;
                     walk_total = __fsub_rn(total, q_draft);
-                    const bool only_draft = (n == 1 && (int32_t)col_at(0) + a.id_offset == draft);
-                    if (only_draft) {
+                    if (n == 1 && draft_idx == 0u) { // nothing but the rejected draft
                         tok = draft;
                         prob = 1.0f;
                     }
                 }
             }
             if (tok < 0) {
-                const float uu = (a.mode == kModeVerify) ? u2_row : u_row;
-                r = __fmul_rn(uu, walk_total);
+                float r = __fmul_rn((a.mode == kModeVerify) ? u2_row : u_row, walk_total);
                 const float eps = 1e-6f * walk_total;
-                int32_t last = -1;
-                float last_q = 0.0f;
-                bool first = true, done = false;
-                for (uint32_t i = 0; i < n && !done; ++i) {
-                    const int32_t id = (int32_t)col_at(i) + a.id_offset;
-                    if (skip_draft && id == draft)
-                        continue;
-                    const float q = q_at(i);
-                    last = id;
-                    last_q = q;
-                    if (r < q) {
-                        tok = id;
-                        prob = __fdiv_rn(q, walk_total);
-                        // boundary below (not for the first candidate) or above (not for the last)
-                        bool more = false;
-                        for (uint32_t j = i + 1; j < n; ++j)
-                            if (!(skip_draft && (int32_t)col_at(j) + a.id_offset == draft))
-                                more = true;
-                        if ((!first && r < eps) || (more && __fsub_rn(q, r) < eps))
-                            flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
-                        done = true;
-                    } else {
-                        r = __fsub_rn(r, q);
-                        first = false;
+                const uint32_t first_valid = (skip_idx == 0u) ? 1u : 0u;
+                const uint32_t last_valid = (skip_idx == n - 1u) ? n - 2u : n - 1u;
+                bool found = false;
+                uint32_t hit = 0;
+                float r_hit = 0.0f, q_hit = 0.0f;
+                for (uint32_t base = 0; base < n && !found; base += 32u) {
+                    float q = 0.0f; // the skipped draft: weight 0 never wins and changes nothing
+                    if (base + lane < n && base + lane != skip_idx)
+                        q = q_of(base + lane);
+                    const int cnt = (int)min(32u, n - base);
+#pragma unroll 8
+                    for (int j = 0; j < cnt; ++j) {
+                        const float qj = __shfl_sync(full, q, j);
+                        if (!found && r < qj) {
+                            found = true;
+                            hit = base + (uint32_t)j;
+                            r_hit = r;
+                            q_hit = qj;
+                        }
+                        r = __fsub_rn(r, qj);
                     }
                 }
-                if (!done) { // rounding: the last candidate (sampler.cpp:72)
-                    tok = last;
-                    prob = __fdiv_rn(last_q, walk_total);
+                float qx;
+                uint32_t cx;
+                if (found) {
+                    fetch(hit, qx, cx);
+                    tok = (int32_t)cx + a.id_offset;
+                    prob = __fdiv_rn(q_hit, walk_total);
+                    // boundary below (not for the first candidate) or above (not for the last)
+                    if ((hit != first_valid && r_hit < eps) || (hit < last_valid && __fsub_rn(q_hit, r_hit) < eps))
+                        flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                } else { // rounding: the last candidate (sampler.cpp:72)
+                    fetch(last_valid, qx, cx);
+                    tok = (int32_t)cx + a.id_offset;
+                    prob = __fdiv_rn(qx, walk_total);
                 }
             }
         }
-        if (a.token) a.token[row] = tok;
-        if (a.prob) a.prob[row] = prob;
-        if (a.flags) a.flags[row] = flags;
-        if (a.n_cand) a.n_cand[row] = n;
-        if (a.accepted) a.accepted[row] = acc;
-        if (a.total_out) a.total_out[row] = total;
-        s.n_final = n;
-        if (a.timing)
-            a.timing[(size_t)row * 64 + 3] = global_ns();
+        if (lane == 0) {
+            if (a.token) a.token[row] = tok;
+            if (a.prob) a.prob[row] = prob;
+            if (a.flags) a.flags[row] = flags;
+            if (a.n_cand) a.n_cand[row] = n;
+            if (a.accepted) a.accepted[row] = acc;
+            if (a.total_out) a.total_out[row] = total;
+            s.n_final = n;
+            if (a.timing)
+                a.timing[(size_t)row * 64 + 3] = global_ns();
+        }
     }
-    __syncthreads();
     if (a.cand_ids || a.cand_q) {
+        __syncthreads();
         const uint32_t nf = min(s.n_final, a.cand_cap);
         for (uint32_t i = tid; i < nf; i += kThreads) {
-            const unsigned long long key = keys[i];
-            const uint32_t col = sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
-            const float q = sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
+            float q;
+            uint32_t col;
+            fetch(i, q, col);
             if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)col + a.id_offset;
             if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + i] = q;
         }
