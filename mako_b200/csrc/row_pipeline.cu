@@ -55,11 +55,18 @@ constexpr int kVec = kTile / (kReaders * 4); // 128-bit loads per reader thread 
 constexpr int kEl = kVec * 4;
 static_assert(kVec * kReaders * 4 == kTile, "a tile is a whole number of 128-bit loads per reader thread");
 constexpr int kHistCap = 4096;  // history entries de-duplicated in shared memory; longer histories scan global memory
-constexpr int kBmWords = 5120;  // history bitmap: one bit per column, vocabularies up to 163840 columns
+#ifndef MK_BM_WORDS
+#define MK_BM_WORDS 5120
+#endif
+constexpr int kBmWords = MK_BM_WORDS;  // history bitmap: one bit per column, vocabularies up to 163840 columns
 constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
 constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) once the streaming is over
-constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
-constexpr int kBinShift = 21;
+#ifndef MK_BINS
+#define MK_BINS 2048
+#define MK_BINSHIFT 21
+#endif
+constexpr int kBins = MK_BINS;     // top_k histogram: 11 leading bits of the order key
+constexpr int kBinShift = MK_BINSHIFT;
 
 struct __align__(128) Smem {
     float ring[kStages][kTile];     // tile ring; after the streaming, with `table`, the sort area of the finish
@@ -217,12 +224,18 @@ __device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t*
 // synchronises before (bitmap complete) and after (wpre complete). Each thread takes a contiguous run of words.
 __device__ __forceinline__ void word_ranks(Smem& s, uint32_t bm_words)
 {
+    constexpr int kWordsPerThread = (kBmWords + kThreads - 1) / kThreads;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t per = (bm_words + kThreads - 1) / kThreads;
-    const uint32_t w0 = min(tid * per, bm_words), w1 = min(w0 + per, bm_words);
+    const uint32_t w0 = min(tid * per, bm_words);
+    uint32_t pc[kWordsPerThread]; // popcounts of this thread's words: all loads in flight together
     uint32_t mine = 0;
-    for (uint32_t w = w0; w < w1; ++w)
-        mine += __popc(s.bitmap[w]);
+#pragma unroll
+    for (int i = 0; i < kWordsPerThread; ++i) {
+        const uint32_t w = w0 + (uint32_t)i;
+        pc[i] = ((uint32_t)i < per && w < bm_words) ? (uint32_t)__popc(s.bitmap[w]) : 0u;
+        mine += pc[i];
+    }
     uint32_t inc = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -237,12 +250,15 @@ __device__ __forceinline__ void word_ranks(Smem& s, uint32_t bm_words)
     uint32_t before = inc - mine;
     for (uint32_t w = 0; w < warp; ++w)
         before += wtot[w];
-    for (uint32_t w = w0; w < w1; ++w) {
-        s.wpre[w] = (uint16_t)before;
-        before += __popc(s.bitmap[w]);
+#pragma unroll
+    for (int i = 0; i < kWordsPerThread; ++i) {
+        const uint32_t w = w0 + (uint32_t)i;
+        if ((uint32_t)i < per && w < bm_words)
+            s.wpre[w] = (uint16_t)before;
+        before += pc[i];
     }
-    if (w1 == bm_words && w0 < w1)
-        s.n_distinct = before; // the thread that holds the last word
+    if (tid == kThreads - 1)
+        s.n_distinct = before; // every word lies at or before the last thread's run
 }
 
 // Bitonic sort of n2 (power of two) 64-bit keys in shared memory by the whole CTA.
@@ -406,6 +422,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     uint32_t tiles_issued = 0;
     __syncthreads();
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 6] = global_ns();
     // The producer fills the ring before anything else, so that the copies fly during the set-up.
     if (a.use_bulk_copy) {
         tiles_issued = min((uint32_t)kStages, n_tiles);
@@ -425,6 +443,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
         }
     }
+    uint32_t own = 0; // this thread's history entries that were the first to name their column
     if (use_table) {
         uint16_t* const wpre = s.wpre;
         // The generated tokens as the reference keeps them (a multiset id -> count, sampler.cpp:15-18), in a form
@@ -438,12 +457,17 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             if (col64 >= 0 && col64 < (int64_t)V) {
                 const uint32_t col = (uint32_t)col64, bit = 1u << (col & 31u);
                 if (!(*(volatile uint32_t*)&s.bitmap[col >> 5] & bit)) // skip the atomic once the bit is visible
-                    atomicOr(&s.bitmap[col >> 5], bit);
+                    if (!(atomicOr(&s.bitmap[col >> 5], bit) & bit))
+                        own |= 1u << hi; // exactly one entry per distinct column sees its bit go from 0 to 1
             }
         }
         __syncthreads();
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 7] = global_ns();
         word_ranks(s, bm_words);
         __syncthreads();
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 8] = global_ns();
 #pragma unroll
         for (int hi = 0; hi < kHistPerThread; ++hi) {
             const uint32_t j = (uint32_t)hi * kThreads + tid;
@@ -462,7 +486,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // together (the first tiles hold the most frequent token ids, by far the largest share of the history), then
     // the fix-up warps carry on alone with the tiles that follow.
     uint32_t prefixed = 0;
-    if ((use_table || nb > 0) && !long_history && tiles_issued > 0) {
+    if (has_fix && !long_history && tiles_issued > 0) {
         prefixed = tiles_issued;
         bool ok = true;
         for (uint32_t t = 0; t < prefixed; ++t)
@@ -482,10 +506,34 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             __syncthreads();
         }
         if (use_table) {
-            const uint32_t w_hi = min((span + 31u) >> 5, bm_words);
-            fix_hits(s.bitmap, s.wpre, s.counts, &s.ring[0][0], 0u, 0u, w_hi, 0u,
-                     (w_hi < bm_words) ? (uint32_t)s.wpre[w_hi] : s.n_distinct, tid, kThreads, cfg);
+            // Every column has one owner among the history entries (the one that set its bitmap bit); the owner
+            // applies the penalties. No search, no atomics: the entry names the column. Written as passes over
+            // the thread's entries, so that the shared-memory reads of all of them are in flight together.
+            float* const ring0 = &s.ring[0][0];
+            uint32_t pc[kHistPerThread], pn[kHistPerThread];
+            float pv[kHistPerThread];
+#pragma unroll
+            for (int hi = 0; hi < kHistPerThread; ++hi) {
+                const uint32_t col = (uint32_t)(hv[hi] - a.id_offset);
+                pc[hi] = (((own >> hi) & 1u) && col < span) ? col : 0xffffffffu;
+                const uint32_t c = (pc[hi] != 0xffffffffu) ? col : 0u;
+                pn[hi] = s.wpre[c >> 5] + __popc(s.bitmap[c >> 5] & ((1u << (c & 31u)) - 1u)); // rank
+                pv[hi] = ring0[c];
+            }
+#pragma unroll
+            for (int hi = 0; hi < kHistPerThread; ++hi)
+                pn[hi] = (s.counts[pn[hi] >> 1] >> ((pn[hi] & 1u) * 16u)) & 0xffffu; // count
+#pragma unroll
+            for (int hi = 0; hi < kHistPerThread; ++hi) {
+                const float v = penalise(pv[hi], pn[hi], cfg);
+                if (pc[hi] != 0xffffffffu)
+                    ring0[pc[hi]] = v;
+            }
         }
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 14] = global_ns();
+        if (a.timing && tid == kThreads - 1)
+            a.timing[(size_t)row * 64 + 15] = global_ns();
         __syncthreads();
     }
     // ---- streaming ----------------------------------------------------------------------------------------------
@@ -763,6 +811,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         return;
     }
 
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 22] = global_ns();
     const bool any_finite = s.best_key != 0ull;
     float m = any_finite ? key_to_float((uint32_t)(s.best_key >> 32)) : -__int_as_float(0x7f800000);
     uint32_t arg_col = any_finite ? (0xffffffffu - (uint32_t)(s.best_key & 0xffffffffull)) : 0u;
@@ -774,6 +824,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (mrow && !any_finite && !s.nan0)
         flags |= MK_FLAG_ALL_MASKED;
 
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 23] = global_ns();
     // need_sum: weight of the uncollected tail (the whole row for a shard record), relative to the row maximum:
     // sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
     double total_approx = 0.0;
@@ -801,6 +853,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         __syncthreads(); // warp_sum is written again below
     }
 
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 24] = global_ns();
     if (a.mode == kModeVpLocal) {
         // Shard record: header {max, n, sum} then the k best (logit, global id), by (logit desc, id asc).
         unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
@@ -863,6 +917,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         return;
     }
 
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 25] = global_ns();
     // exact weights of the collected elements, min_p filter (sampler.cpp:33-35)
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
     const uint32_t n_raw = min(s.ncand, a.scratch_cap);
@@ -871,6 +927,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (!s.nan0) {
         // Elements collected while the running maximum was still low are dropped by the final bound first.
         float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 26] = global_ns();
         if (cfg.need_sum && n_raw > 1024u) {
             // top_p alone: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was not
             // collected belongs to that tail; collected elements can join it from the bottom for as long as the
@@ -949,6 +1007,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
         double exact = 0.0;
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 20] = global_ns();
         for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
             uint2 cv[4]; // four loads in flight
 #pragma unroll
@@ -973,6 +1033,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
         }
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 21] = global_ns();
         if (cfg.need_sum) {
             // top_p's total (sampler.cpp:45-47) covers every column: exact weights for all that was collected, the
             // approximate sum for the rest. The margin that goes with it is 1e-5 of the approximate part plus the
@@ -1331,11 +1393,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     const bool cut_k = cfg.top_k > 0 && cfg.top_k < n;       // sampler.cpp:39
     const bool sorted = cut_k || cfg.use_topp;               // else ascending id
+    constexpr bool kOrdFits = sizeof(Smem::counts) + sizeof(Smem::hist) >= kSortCap * sizeof(uint16_t);
     // Ascending id needs no sort: a bitmap of the candidates' columns ranks them, and `ord` lists the candidates'
     // slots by rank. (Vocabularies beyond the bitmap, and lists too short to be worth it, sort by column.)
-    const bool by_rank = !sorted && V <= kMaxBitmapVocab && n > 64u;
+    const bool by_rank = kOrdFits && !sorted && V <= kMaxBitmapVocab && n > 64u;
     static_assert(offsetof(Smem, hist) == offsetof(Smem, counts) + sizeof(Smem::counts), "ord spans counts and hist");
-    static_assert(sizeof(Smem::counts) + sizeof(Smem::hist) >= kSortCap * sizeof(uint16_t), "ord holds kSortCap slots");
     uint16_t* const ord = reinterpret_cast<uint16_t*>(s.counts);
     if (by_rank) {
         const uint32_t words = (V + 31u) >> 5;
@@ -1372,6 +1434,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         if (n > 1)
             block_sort(keys, n2);
     }
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 12] = global_ns();
     // the r-th candidate of the list in the reference's order
     auto fetch = [&](uint32_t r, float& q, uint32_t& col) {
         if (sorted) {
@@ -1477,6 +1541,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         n = max(k, 1u);
     }
 
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 13] = global_ns();
     // Float total and the walk, left to right in the reference's order and precision (sampler.cpp:64-73, 80-83,
     // 100-106), by one warp: every lane loads one candidate, the values go round by shuffle and every lane runs
     // the same sequential chain, so the chain never waits for memory.
