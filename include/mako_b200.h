@@ -182,11 +182,10 @@ int mk_row_sampler_verify(mk_row_sampler* r, const float* logits, int32_t draft,
 int mk_debug_expf(const float* x_dev, float* y_dev, uint64_t n, void* stream);
 
 /* Profiling hook: when timing_dev (device, [max_batch][64] uint64) is non-NULL, each row's CTA of the following
- * sample/verify launches stores %globaltimer nanosecond stamps: [0] start, [1] set-up done, [2] streaming done,
- * [3] end, [4..] steps inside the set-up. */
+ * sample/verify launches stores %globaltimer nanosecond stamps: [0] start, [1] set-up done, [2] last tile requested,
+ * [3] end; inside the set-up [6] memory cleared, [7] bitmap, [8] ranks, [4] counts, [5] first tiles landed; inside
+ * the finish [11] candidates filtered ([9] collected, [10] kept: counts, not times), [12] ordered, [13] top_p done. */
 int mk_debug_set_timing(mk_sampler* s, unsigned long long* timing_dev);
-/* Profiling hook: switches parts of the row kernel off to time the rest (results are then wrong). 0 = normal. */
-int mk_debug_set_flags(mk_sampler* s, uint32_t flags);
 
 /* Bytes the roofline counts for one row: logits once + history + mask + bias + uniforms + outputs. */
 uint64_t mk_row_bytes(uint32_t n_vocab, uint32_t n_history, int has_mask, uint32_t n_bias, uint32_t n_uniforms);

@@ -116,7 +116,6 @@ def _load() -> C.CDLL:
     lib.mk_row_sampler_verify.argtypes = [vp, vp, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.mk_debug_expf.argtypes = [vp, vp, C.c_uint64, vp]
     lib.mk_debug_set_timing.argtypes = [vp, vp]
-    lib.mk_debug_set_flags.argtypes = [vp, C.c_uint32]
     return lib
 
 

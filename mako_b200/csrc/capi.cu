@@ -56,7 +56,6 @@ struct mk_sampler {
     int32_t* p_tok = nullptr;
     // host-buffer staging (sized on first use)
     cudaStream_t own_stream = nullptr;
-    uint32_t dbg = 0;
     unsigned long long* timing = nullptr; // debug: per-row phase timestamps of the next launches
     unsigned char* stage = nullptr;
     size_t stage_bytes = 0;
@@ -130,7 +129,6 @@ void fill_common(mk::RowKernelArgs& a, const mk_sampler* s, const mk_rows* r)
     a.scratch = s->scratch;
     a.scratch_cap = scratch_cap(s->n_vocab);
     a.timing = s->timing;
-    a.dbg = s->dbg;
     a.use_bulk_copy = ((reinterpret_cast<uintptr_t>(r->logits) & 15u) == 0 && (r->ld % 4u) == 0) ? 1 : 0;
 }
 
@@ -224,7 +222,7 @@ int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t m
         if (e == cudaSuccess)
             e = cudaMalloc(p, bytes);
     };
-    alloc((void**)&s->scratch, b * (size_t)scratch_cap(n_vocab) * 16);
+    alloc((void**)&s->scratch, b * mk::row_scratch_words(scratch_cap(n_vocab)) * 4);
     alloc((void**)&s->p_ids, b * kPqCap * 4);
     alloc((void**)&s->q_ids, b * kPqCap * 4);
     alloc((void**)&s->p_q, b * kPqCap * 4);
@@ -285,7 +283,7 @@ int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, 
 // in this file-scope device array instead of a handle's buffer: MK_STATIC_MAX_ROWS rows of 16 bytes per column
 // for vocabularies up to MK_STATIC_MAX_VOCAB, about 20 MiB on every GPU that loads the library, held until the
 // process exits. The symbol is a host-side stand-in here; the address the kernel needs is asked for once per device.
-static __device__ __align__(256) uint32_t g_static_scratch[(size_t)MK_STATIC_MAX_ROWS * 4u * MK_STATIC_MAX_VOCAB];
+static __device__ __align__(256) uint32_t g_static_scratch[(size_t)MK_STATIC_MAX_ROWS * (4u * MK_STATIC_MAX_VOCAB + 4u)];
 static uint32_t* g_static_scratch_ptr[64] = {};
 
 int mk_sample_rows_static(int device, const mk_rows* rows, const float* u, const mk_sample_out* out, void* stream)
@@ -541,13 +539,6 @@ int mk_sampler_sample_host(mk_sampler* s, const mk_rows* hr, const float* u, con
     return MK_OK;
 }
 
-int mk_debug_set_flags(mk_sampler* s, uint32_t flags)
-{
-    if (!s)
-        return fail(MK_ERR_INVALID_ARGUMENT, "null sampler handle");
-    s->dbg = flags;
-    return MK_OK;
-}
 
 int mk_debug_set_timing(mk_sampler* s, unsigned long long* timing_dev)
 {

@@ -45,7 +45,7 @@ namespace mk {
 namespace {
 
 constexpr int kTile = MK_TILE;   // floats per tile
-constexpr int kStages = MK_STAGES;
+constexpr int kMaxStages = 7;  // ring stages that fit when a row needs no tables
 constexpr int kProducerThreads = 32;
 constexpr int kFixers = 64;
 constexpr int kReaders = 256;
@@ -65,17 +65,17 @@ constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) 
 #define MK_BINS 2048
 #define MK_BINSHIFT 21
 #endif
+constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates kept
 constexpr int kBins = MK_BINS;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = MK_BINSHIFT;
 
+// Shared memory of a CTA: this fixed head, then kDynBytes laid out per row. While the row streams: the tables the
+// row needs (generated-column bitmap, per-word ranks, counts; the top_k histogram) and, in all that is left, the
+// tile ring — five stages beside a history's tables, seven without. Once the streaming is over the same bytes hold
+// the finish's sort keys and its own bitmap, ranks and order list.
 struct __align__(128) Smem {
-    float ring[kStages][kTile];     // tile ring; after the streaming, with `table`, the sort area of the finish
-    uint32_t bitmap[kBmWords];      // bit c set: column c was generated (long histories: per-tile id counters)
-    uint32_t counts[kHistCap / 2];  // occurrences per distinct generated column, by rank, two 16-bit counters a word
-    uint32_t hist[kBins];           // top_k: counts per key bin
-    uint16_t wpre[kBmWords];        // set bits before each bitmap word = rank of its first generated column
     double warp_sum[kThreads / 32];
-    uint64_t full[kStages], ready[kStages], empty[kStages];
+    uint64_t full[kMaxStages], ready[kMaxStages], empty[kMaxStages];
     unsigned long long best_key;    // (order key of the row maximum << 32) | ~column: first argmax wins
     uint32_t m_key;                 // running maximum, as order key
     uint32_t thr_topk_key;          // top_k lower bound, as order key (only ever raised)
@@ -88,13 +88,23 @@ struct __align__(128) Smem {
     uint32_t flags;
     uint32_t n_distinct;            // distinct generated columns
 };
+constexpr uint32_t kSmemBytes = 115712; // two CTAs per SM: (228 KB - 2 x 1 KB reserved) / 2
+constexpr uint32_t kHeadBytes = (sizeof(Smem) + 127u) & ~127u;
+constexpr uint32_t kDynBytes = kSmemBytes - kHeadBytes;
+// finish-phase layout inside the dynamic part
+constexpr uint32_t kOffKeys = 0;                                  // kSortCap 64-bit keys
+constexpr uint32_t kOffFinBitmap = kSortCap * 8u;                 // kBmWords words (also: the mass histogram)
+constexpr uint32_t kOffFinWpre = kOffFinBitmap + kBmWords * 4u;   // kBmWords 16-bit ranks
+constexpr uint32_t kOffFinOrd = kOffFinWpre + kBmWords * 2u;      // kSortCap 16-bit slots
+static_assert(kOffFinOrd + kSortCap * 2u <= kDynBytes, "finish layout fits");
+static_assert(kBins * 4u <= kBmWords * 4u, "mass histogram fits the finish bitmap area");
 
 struct RowCfg {
     float temperature, inv_t, minp_eff, top_p;
     uint32_t top_k;
     uint32_t hist_k;    // the histogram bound keeps the hist_k largest elements
     float rep, presence, frequency;
-    bool greedy, hist_mode, need_sum, use_topp, pen_active;
+    bool greedy, hist_mode, need_sum, use_topp, pen_active, optimistic;
     float delta_w;      // keep elements with l >= running max - delta_w
     bool force_none;    // inv_t is inf/NaN: no finite weight can exist
 };
@@ -114,7 +124,7 @@ __device__ __forceinline__ float warp_max(float v)
     return v;
 }
 
-__device__ __forceinline__ RowCfg make_cfg(const mk_sampling_params& p, uint32_t n_vocab, int mode, uint32_t vp_k)
+__device__ __forceinline__ RowCfg make_cfg(const mk_sampling_params& p, uint32_t n_vocab, int mode, uint32_t vp_k, int pass)
 {
     RowCfg c;
     c.temperature = p.temperature;
@@ -136,6 +146,14 @@ __device__ __forceinline__ RowCfg make_cfg(const mk_sampling_params& p, uint32_t
     // The float total over "all candidates" is only needed when top_p is the only truncation.
     c.need_sum = !c.greedy && c.use_topp && !minp_on && !c.hist_mode;
     c.force_none = !c.greedy && (!(c.inv_t < __int_as_float(0x7f800000)) || !(c.inv_t == c.inv_t));
+    // top_p alone: the first launch bets that the nucleus lies within the kNucleusGuess largest elements and keeps
+    // only those (the top_k histogram bound, with no top_k cut afterwards); a row whose nucleus does not close within
+    // what was kept asks for the second pass, which keeps everything the mass bound allows.
+    c.optimistic = c.need_sum && pass == 0 && mode != kModeVpLocal && kNucleusGuess < n_vocab;
+    if (c.optimistic) {
+        c.hist_mode = true;
+        c.hist_k = kNucleusGuess;
+    }
     if (mode == kModeVpLocal) {
         c.hist_mode = vp_k < n_vocab;
         c.top_k = vp_k;
@@ -219,10 +237,10 @@ __device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t*
     }
 }
 
-// Exclusive prefix of the per-word popcounts of s.bitmap[0, bm_words) into s.wpre, total into s.n_distinct: a set
+// Exclusive prefix of the per-word popcounts of bitmap[0, bm_words) into wpre, total into s.n_distinct: a set
 // bit's rank among all set bits is then wpre[word] + popcount of the lower bits of its word. Whole CTA; the caller
 // synchronises before (bitmap complete) and after (wpre complete). Each thread takes a contiguous run of words.
-__device__ __forceinline__ void word_ranks(Smem& s, uint32_t bm_words)
+__device__ __forceinline__ void word_ranks(Smem& s, const uint32_t* bitmap, uint16_t* wpre, uint32_t bm_words)
 {
     constexpr int kWordsPerThread = (kBmWords + kThreads - 1) / kThreads;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -233,7 +251,7 @@ __device__ __forceinline__ void word_ranks(Smem& s, uint32_t bm_words)
 #pragma unroll
     for (int i = 0; i < kWordsPerThread; ++i) {
         const uint32_t w = w0 + (uint32_t)i;
-        pc[i] = ((uint32_t)i < per && w < bm_words) ? (uint32_t)__popc(s.bitmap[w]) : 0u;
+        pc[i] = ((uint32_t)i < per && w < bm_words) ? (uint32_t)__popc(bitmap[w]) : 0u;
         mine += pc[i];
     }
     uint32_t inc = mine;
@@ -254,7 +272,7 @@ __device__ __forceinline__ void word_ranks(Smem& s, uint32_t bm_words)
     for (int i = 0; i < kWordsPerThread; ++i) {
         const uint32_t w = w0 + (uint32_t)i;
         if ((uint32_t)i < per && w < bm_words)
-            s.wpre[w] = (uint16_t)before;
+            wpre[w] = (uint16_t)before;
         before += pc[i];
     }
     if (tid == kThreads - 1)
@@ -353,7 +371,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const uint32_t n_tiles = (V + kTile - 1) / kTile;
     const float* __restrict__ lrow = a.logits + (size_t)row * a.ld;
     const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
-    const RowCfg cfg = make_cfg(prm, V, a.mode, a.vp_k);
+    const RowCfg cfg = make_cfg(prm, V, a.mode, a.vp_k, a.pass);
 
     const uint32_t hlen_all = a.history ? (a.history_len ? (uint32_t)max(a.history_len[row], 0) : a.n_history) : 0u;
     const bool has_hist = !cfg.greedy && cfg.pen_active && hlen_all > 0;
@@ -367,8 +385,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // Per-row scratch, 16 bytes per column: scratch_cap raw candidates (logit bits, column) — sorted in place as
     // 64-bit keys by the large sorted-list path — then as much again: the merge sort's second buffer, or (large
     // unsorted lists) one float per column.
-    uint2* __restrict__ scratch = reinterpret_cast<uint2*>(a.scratch + (size_t)row * 4u * a.scratch_cap);
-    float* __restrict__ qrow = reinterpret_cast<float*>(a.scratch + (size_t)row * 4u * a.scratch_cap + 2u * a.scratch_cap);
+    uint32_t* const row_scratch = a.scratch + (size_t)row * row_scratch_words(a.scratch_cap);
+    uint2* __restrict__ scratch = reinterpret_cast<uint2*>(row_scratch);
+    float* __restrict__ qrow = reinterpret_cast<float*>(row_scratch + 2u * a.scratch_cap);
+    uint32_t* const again = row_scratch + 4u * a.scratch_cap; // set by the first launch: this row wants the second pass
+    if (a.pass == 1 && again[0] == 0u)
+        return;
+    if (a.pass == 0 && tid == 0)
+        again[0] = 0u;
 
     const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
     const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
@@ -384,11 +408,27 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             hv[i] = (j < hlen) ? __ldg(hrow + j) : 0;
         }
     }
+    // ---- shared-memory layout of the streaming phase ---------------------------------------------------------------
+    const bool use_table = has_hist && !long_history;
+    const uint32_t bm_words = (V + 31u) / 32u;
+    unsigned char* const dyn = smem_raw + kHeadBytes;
+    uint32_t off = 0;
+    uint32_t* const bitmap = reinterpret_cast<uint32_t*>(dyn + off); // long histories: per-tile id counters instead
+    off += use_table ? ((bm_words * 4u + 15u) & ~15u) : (long_history ? (uint32_t)kTile * 2u : 0u);
+    uint16_t* const wpre = reinterpret_cast<uint16_t*>(dyn + off);
+    off += use_table ? ((bm_words * 2u + 15u) & ~15u) : 0u;
+    uint32_t* const counts = reinterpret_cast<uint32_t*>(dyn + off);
+    off += use_table ? (uint32_t)kHistCap * 2u : 0u;
+    uint32_t* const hist = reinterpret_cast<uint32_t*>(dyn + off);
+    off += cfg.hist_mode ? (uint32_t)kBins * 4u : 0u;
+    off = (off + 127u) & ~127u;
+    float* const ring = reinterpret_cast<float*>(dyn + off);
+    const uint32_t n_stages = min((uint32_t)kMaxStages, (kDynBytes - off) / ((uint32_t)kTile * 4u)); // >= 4
     // ---- set-up -------------------------------------------------------------------------------------------------
     if (a.timing && tid == 0)
         a.timing[(size_t)row * 64 + 0] = global_ns();
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < kMaxStages; ++i) {
             mbar_init(&s.full[i], 1);
             mbar_init(&s.ready[i], 1);
             mbar_init(&s.empty[i], kReaderWarps);
@@ -405,20 +445,18 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         s.flags = 0;
         fence_barrier_init();
     }
-    uint32_t* const cnt = s.bitmap; // long histories: per-tile id counters (two 16-bit counters per word)
-    const bool use_table = has_hist && !long_history;
-    const uint32_t bm_words = (V + 31u) / 32u;
+    uint32_t* const cnt = bitmap; // long histories: per-tile id counters (two 16-bit counters per word)
     if (long_history)
         for (uint32_t i = tid; i < kTile / 2; i += kThreads)
             cnt[i] = 0;
     if (cfg.hist_mode)
         for (uint32_t i = tid; i < kBins; i += kThreads)
-            s.hist[i] = 0;
+            hist[i] = 0;
     if (use_table) {
         for (uint32_t i = tid; i < bm_words; i += kThreads)
-            s.bitmap[i] = 0;
+            bitmap[i] = 0;
         for (uint32_t i = tid; i < kHistCap / 2; i += kThreads)
-            s.counts[i] = 0;
+            counts[i] = 0;
     }
     uint32_t tiles_issued = 0;
     __syncthreads();
@@ -426,17 +464,17 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         a.timing[(size_t)row * 64 + 6] = global_ns();
     // The producer fills the ring before anything else, so that the copies fly during the set-up.
     if (a.use_bulk_copy) {
-        tiles_issued = min((uint32_t)kStages, n_tiles);
+        tiles_issued = min(n_stages, n_tiles);
         if (tid == 0) {
             for (uint32_t t = 0; t < tiles_issued; ++t) {
                 const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
                 const uint32_t bytes = (n_t * 4u) & ~15u;
                 const float* src = lrow + (size_t)t * kTile;
                 for (uint32_t e = bytes / 4; e < n_t; ++e)
-                    s.ring[t][e] = src[e];
+                    ring[t * kTile + e] = src[e];
                 if (bytes > 0) {
                     mbar_arrive_expect_tx(&s.full[t], bytes);
-                    bulk_load(s.ring[t], src, bytes, &s.full[t]);
+                    bulk_load(ring + t * kTile, src, bytes, &s.full[t]);
                 } else {
                     mbar_arrive(&s.full[t]);
                 }
@@ -445,7 +483,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     uint32_t own = 0; // this thread's history entries that were the first to name their column
     if (use_table) {
-        uint16_t* const wpre = s.wpre;
         // The generated tokens as the reference keeps them (a multiset id -> count, sampler.cpp:15-18), in a form
         // the readers can consult per column without searching: a bitmap of generated columns, the number of set
         // bits before each bitmap word (so a column's rank among the distinct ones is one popcount away), and the
@@ -456,15 +493,15 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             const int64_t col64 = (j < hlen) ? ((int64_t)hv[hi] - a.id_offset) : -1;
             if (col64 >= 0 && col64 < (int64_t)V) {
                 const uint32_t col = (uint32_t)col64, bit = 1u << (col & 31u);
-                if (!(*(volatile uint32_t*)&s.bitmap[col >> 5] & bit)) // skip the atomic once the bit is visible
-                    if (!(atomicOr(&s.bitmap[col >> 5], bit) & bit))
+                if (!(*(volatile uint32_t*)&bitmap[col >> 5] & bit)) // skip the atomic once the bit is visible
+                    if (!(atomicOr(&bitmap[col >> 5], bit) & bit))
                         own |= 1u << hi; // exactly one entry per distinct column sees its bit go from 0 to 1
             }
         }
         __syncthreads();
         if (a.timing && tid == 0)
             a.timing[(size_t)row * 64 + 7] = global_ns();
-        word_ranks(s, bm_words);
+        word_ranks(s, bitmap, wpre, bm_words);
         __syncthreads();
         if (a.timing && tid == 0)
             a.timing[(size_t)row * 64 + 8] = global_ns();
@@ -474,8 +511,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             const int64_t col64 = (j < hlen) ? ((int64_t)hv[hi] - a.id_offset) : -1;
             if (col64 >= 0 && col64 < (int64_t)V) {
                 const uint32_t col = (uint32_t)col64;
-                const uint32_t rank = wpre[col >> 5] + __popc(s.bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
-                atomicAdd(&s.counts[rank >> 1], 1u << ((rank & 1u) * 16u));
+                const uint32_t rank = wpre[col >> 5] + __popc(bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
+                atomicAdd(&counts[rank >> 1], 1u << ((rank & 1u) * 16u));
             }
         }
         __syncthreads();
@@ -501,7 +538,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 const mk_bias be = brow[j];
                 const int64_t loc = (int64_t)be.id - a.id_offset;
                 if (be.id >= 0 && loc >= 0 && loc < (int64_t)span)
-                    s.ring[0][loc] = __fadd_rn(s.ring[0][loc], be.value); // stages 0.. are contiguous
+                    ring[loc] = __fadd_rn(ring[loc], be.value); // stages 0.. are contiguous
             }
             __syncthreads();
         }
@@ -509,7 +546,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             // Every column has one owner among the history entries (the one that set its bitmap bit); the owner
             // applies the penalties. No search, no atomics: the entry names the column. Written as passes over
             // the thread's entries, so that the shared-memory reads of all of them are in flight together.
-            float* const ring0 = &s.ring[0][0];
+            float* const ring0 = ring;
             uint32_t pc[kHistPerThread], pn[kHistPerThread];
             float pv[kHistPerThread];
 #pragma unroll
@@ -517,12 +554,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 const uint32_t col = (uint32_t)(hv[hi] - a.id_offset);
                 pc[hi] = (((own >> hi) & 1u) && col < span) ? col : 0xffffffffu;
                 const uint32_t c = (pc[hi] != 0xffffffffu) ? col : 0u;
-                pn[hi] = s.wpre[c >> 5] + __popc(s.bitmap[c >> 5] & ((1u << (c & 31u)) - 1u)); // rank
+                pn[hi] = wpre[c >> 5] + __popc(bitmap[c >> 5] & ((1u << (c & 31u)) - 1u)); // rank
                 pv[hi] = ring0[c];
             }
 #pragma unroll
             for (int hi = 0; hi < kHistPerThread; ++hi)
-                pn[hi] = (s.counts[pn[hi] >> 1] >> ((pn[hi] & 1u) * 16u)) & 0xffffu; // count
+                pn[hi] = (counts[pn[hi] >> 1] >> ((pn[hi] & 1u) * 16u)) & 0xffffu; // count
 #pragma unroll
             for (int hi = 0; hi < kHistPerThread; ++hi) {
                 const float v = penalise(pv[hi], pn[hi], cfg);
@@ -530,10 +567,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     ring0[pc[hi]] = v;
             }
         }
-        if (a.timing && tid == 0)
-            a.timing[(size_t)row * 64 + 14] = global_ns();
-        if (a.timing && tid == kThreads - 1)
-            a.timing[(size_t)row * 64 + 15] = global_ns();
         __syncthreads();
     }
     // ---- streaming ----------------------------------------------------------------------------------------------
@@ -545,9 +578,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 
     if (warp == 0) {
         // producer
-        for (uint32_t t = tiles_issued; t < n_tiles; ++t) {
-            const uint32_t st = t % kStages, k = t / kStages;
-            float* dst = s.ring[st];
+        // tile t lives in stage t % n_stages, k = t / n_stages; the loop starts at 0 or, after a full prologue, at n_stages
+        uint32_t st = (tiles_issued == n_stages) ? 0u : tiles_issued, k = (tiles_issued == n_stages) ? 1u : 0u;
+        for (uint32_t t = tiles_issued; t < n_tiles; ++t, ++st) {
+            if (st == n_stages) {
+                st = 0;
+                ++k;
+            }
+            float* dst = ring + st * kTile;
             const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
             const float* src = lrow + (size_t)t * kTile;
             if (k > 0) {
@@ -599,9 +637,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             if (!long_history)
                 t_first += (fw + (kFixers / 32) - (prefixed % (kFixers / 32))) % (kFixers / 32); // t % 2 == fw
             const bool idle = long_history && fw != 0;
-            for (uint32_t t = t_first; t < n_tiles && !idle; t += t_step) {
-                const uint32_t st = t % kStages, k = t / kStages;
-                float* tp = s.ring[st];
+            uint32_t st = t_first % n_stages, k = t_first / n_stages;
+            for (uint32_t t = t_first; t < n_tiles && !idle; t += t_step, st += t_step) {
+                if (st >= n_stages) {
+                    st -= n_stages;
+                    ++k;
+                }
+                float* tp = ring + st * kTile;
                 const uint32_t base = t * kTile;
                 const uint32_t n_t = min((uint32_t)kTile, V - base);
                 if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
@@ -617,8 +659,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
                 if (use_table) {
                     const uint32_t w_lo = base >> 5, w_hi = min((base + n_t + 31u) >> 5, bm_words);
-                    fix_hits(s.bitmap, s.wpre, s.counts, tp, base, w_lo, w_hi, (uint32_t)s.wpre[w_lo],
-                             (w_hi < bm_words) ? (uint32_t)s.wpre[w_hi] : s.n_distinct, lane, 32u, cfg);
+                    fix_hits(bitmap, wpre, counts, tp, base, w_lo, w_hi, (uint32_t)wpre[w_lo],
+                             (w_hi < bm_words) ? (uint32_t)wpre[w_hi] : s.n_distinct, lane, 32u, cfg);
                 } else if (has_hist) {
                     // long history: count the tile's ids in 16-bit counters, then the first lane to clear a
                     // counter owns that id and applies the penalties with its count
@@ -654,24 +696,34 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         const bool collect = !cfg.greedy || a.mode == kModeVpLocal;
         const bool sum_all = a.mode == kModeVpLocal;
         float warp_pub = ninf;
-        for (uint32_t t = 0; t < n_tiles; ++t) {
-            const uint32_t st = t % kStages, k = t / kStages;
+        uint32_t mw_next[kVec];
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            const uint32_t i0 = j * 1024 + rt * 4;
+            mw_next[j] = mrow ? ((i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u) : 0xffffffffu;
+        }
+        uint32_t st = 0, k = 0;
+        for (uint32_t t = 0; t < n_tiles; ++t, ++st) {
+            if (st == n_stages) {
+                st = 0;
+                ++k;
+            }
             const uint32_t base = t * kTile;
-            uint32_t mw[kVec];
+            uint32_t mw[kVec]; // this tile's mask words were requested a tile ago
 #pragma unroll
             for (int j = 0; j < kVec; ++j)
-                mw[j] = 0xffffffffu;
+                mw[j] = mw_next[j];
             if (mrow) {
 #pragma unroll
                 for (int j = 0; j < kVec; ++j) {
-                    const uint32_t i0 = base + j * 1024 + rt * 4;
-                    mw[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
+                    const uint32_t i0 = base + kTile + j * 1024 + rt * 4;
+                    mw_next[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
                 }
             }
             if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
                 atomicExch(&s.abort_flag, 1u); // keep walking: the named barriers below must stay matched
             float w[kEl];
-            const float4* tp4 = reinterpret_cast<const float4*>(s.ring[st]);
+            const float4* tp4 = reinterpret_cast<const float4*>(ring + st * kTile);
 #pragma unroll
             for (int j = 0; j < kVec; ++j) {
                 const float4 v = tp4[j * 256 + rt];
@@ -726,29 +778,28 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
             float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
-            if (cfg.need_sum && best > ninf) {
-                // Approximate weight of what is NOT collected below (a shard record sums everything): the collected
-                // elements get exact weights in the finish, so only the far tail carries the approximation.
-                if (best > old_best)
-                    sum_acc *= (double)exp2f((old_best - best) * c2);
-                float p = 0.0f;
-#pragma unroll
-                for (int e = 0; e < kEl; ++e)
-                    p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
-                sum_acc += (double)p;
-            }
             if (cfg.hist_mode) {
                 // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
                 // where the count from the top reaches k bounds the k-th largest from below.
                 thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
                 if (tm >= thr) {
+                    // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
+                    // valid one too (bounds only rise), and one pass over the 16 elements costs half of two
+                    uint32_t top_bin = 0;
 #pragma unroll
                     for (int e = 0; e < kEl; ++e)
                         if (w[e] >= thr) {
                             const uint32_t bin = order_key(w[e]) >> kBinShift;
-                            atomicAdd(&s.hist[bin], 1u);
-                            atomicMax(&s.hi_group, bin >> 5);
+                            atomicAdd(&hist[bin], 1u);
+                            top_bin = max(top_bin, bin);
+                            if (collect) {
+                                const uint32_t slot = atomicAdd(&s.ncand, 1u);
+                                if (slot < a.scratch_cap)
+                                    scratch[slot] = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                            }
                         }
+                    if ((top_bin >> 5) > *(volatile uint32_t*)&s.hi_group)
+                        atomicMax(&s.hi_group, top_bin >> 5);
                 }
                 // One reader warp per tile rescans the histogram and raises the bound; nobody waits for it. Counts
                 // only grow and every count is an element at or above its bin's edge, so a bound read from a
@@ -758,7 +809,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     uint32_t cum = 0;
                     int found = -1;
                     for (int g = (int)*(volatile uint32_t*)&s.hi_group; g >= 0 && found < 0; --g) {
-                        const uint32_t cbin = ((volatile uint32_t*)s.hist)[g * 32 + lane];
+                        const uint32_t cbin = ((volatile uint32_t*)hist)[g * 32 + lane];
                         uint32_t suf = cbin; // suffix sum over lanes >= lane
 #pragma unroll
                         for (int o = 1; o < 32; o <<= 1) {
@@ -775,9 +826,20 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     if (lane == 0 && found > 0)
                         atomicMax(&s.thr_topk_key, (uint32_t)found << kBinShift);
                 }
-                thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
             }
-            if (collect && tm >= thr) {
+            if (cfg.need_sum && best > ninf) {
+                // Approximate weight of what is NOT collected (`thr` is the bound the collection used; a shard record
+                // sums everything): the collected
+                // elements get exact weights in the finish, so only the far tail carries the approximation.
+                if (best > old_best)
+                    sum_acc *= (double)exp2f((old_best - best) * c2);
+                float p = 0.0f;
+#pragma unroll
+                for (int e = 0; e < kEl; ++e)
+                    p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
+                sum_acc += (double)p;
+            }
+            if (collect && !cfg.hist_mode && tm >= thr) {
 #pragma unroll
                 for (int e = 0; e < kEl; ++e)
                     if (w[e] >= thr) {
@@ -811,8 +873,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         return;
     }
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 22] = global_ns();
     const bool any_finite = s.best_key != 0ull;
     float m = any_finite ? key_to_float((uint32_t)(s.best_key >> 32)) : -__int_as_float(0x7f800000);
     uint32_t arg_col = any_finite ? (0xffffffffu - (uint32_t)(s.best_key & 0xffffffffull)) : 0u;
@@ -824,8 +884,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (mrow && !any_finite && !s.nan0)
         flags |= MK_FLAG_ALL_MASKED;
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 23] = global_ns();
     // need_sum: weight of the uncollected tail (the whole row for a shard record), relative to the row maximum:
     // sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
     double total_approx = 0.0;
@@ -853,11 +911,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         __syncthreads(); // warp_sum is written again below
     }
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 24] = global_ns();
     if (a.mode == kModeVpLocal) {
         // Shard record: header {max, n, sum} then the k best (logit, global id), by (logit desc, id asc).
-        unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
+        unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
         const uint32_t n_all = min(s.ncand, a.scratch_cap);
         const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         for (uint32_t i = tid; i < n_all; i += kThreads) {
@@ -917,24 +973,20 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         return;
     }
 
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 25] = global_ns();
     // exact weights of the collected elements, min_p filter (sampler.cpp:33-35)
-    unsigned long long* keys = reinterpret_cast<unsigned long long*>(&s.ring[0][0]);
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
     const uint32_t n_raw = min(s.ncand, a.scratch_cap);
     bool overflow = s.ncand > a.scratch_cap;
     double total_need = 0.0, band_need = 0.0; // need_sum: the row total that top_p scales, and its margin
     if (!s.nan0) {
         // Elements collected while the running maximum was still low are dropped by the final bound first.
         float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
-        if (a.timing && tid == 0)
-            a.timing[(size_t)row * 64 + 26] = global_ns();
-        if (cfg.need_sum && n_raw > 1024u) {
+        if (cfg.need_sum && n_raw > 4096u) {
             // top_p alone: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was not
             // collected belongs to that tail; collected elements can join it from the bottom for as long as the
             // tail stays within the budget. Approximate weights decide the cut (with margins); the nucleus itself
             // is then computed from exact weights, and a cut that turns out too tight is reported.
-            float* fh = reinterpret_cast<float*>(s.hist);
+            float* fh = reinterpret_cast<float*>(dyn + kOffFinBitmap);
             for (uint32_t i = tid; i < kBins; i += kThreads)
                 fh[i] = 0.0f;
             if (tid == 0)
@@ -1007,8 +1059,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
         double exact = 0.0;
-        if (a.timing && tid == 0)
-            a.timing[(size_t)row * 64 + 20] = global_ns();
         for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
             uint2 cv[4]; // four loads in flight
 #pragma unroll
@@ -1033,8 +1083,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
         }
-        if (a.timing && tid == 0)
-            a.timing[(size_t)row * 64 + 21] = global_ns();
         if (cfg.need_sum) {
             // top_p's total (sampler.cpp:45-47) covers every column: exact weights for all that was collected, the
             // approximate sum for the rest. The margin that goes with it is 1e-5 of the approximate part plus the
@@ -1078,7 +1126,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
         __threadfence_block();
         __syncthreads();
-        float* stage = &s.ring[0][0];
+        float* stage = reinterpret_cast<float*>(dyn + kOffKeys);
         const int32_t draft_col = (a.mode == kModeVerify) ? (draft_row - a.id_offset) : -1;
         float total = 0.0f, q_draft = 0.0f;
         // pass 0: float total (and the draft's weight); pass 1: the walk
@@ -1189,11 +1237,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
         return;
     }
+    const unsigned long long* ksrc = keys; // the ordered list: shared memory, or the row's scratch for a long one
+    bool pre_sorted = false;
     if (!overflow && n > (uint32_t)kSortCap && a.mode != kModeDistOnly) {
         // More candidates than the shared-memory sort holds, and a truncation that orders them (the unordered case
         // returned above): a flat row under top_p, or a very large top_k. The candidates are sorted in global
         // memory — 8192-key runs in shared memory, then merge passes between the two halves of the row's scratch —
-        // and one thread walks the sorted list through shared-memory tiles, in the reference's order and precision.
+        // and the steps below read the list from there.
         unsigned long long* KA = reinterpret_cast<unsigned long long*>(scratch) + a.scratch_cap; // second half
         unsigned long long* KB = reinterpret_cast<unsigned long long*>(scratch);                 // over the raw list
         const float thr2 = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
@@ -1231,147 +1281,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
             P = src;
         }
-        const bool cut_k2 = cfg.top_k > 0 && cfg.top_k < n;
-        uint32_t n_list = cut_k2 ? cfg.top_k : n;
-        if (cut_k2 && tid == 0) {
-            // weights equal to the k-th may exist below the histogram bound, where nothing was collected
-            const float qk = __uint_as_float(~(uint32_t)(P[cfg.top_k - 1] >> 32));
-            const float edge = key_to_float(s.thr_topk_key);
-            if (edge > -FLT_MAX && expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t)) >= qk)
-                flags |= MK_FLAG_GUARD_BAND;
-        }
-        // thread 0 walks `count` keys in order, a 4096-key tile at a time; body returns true to stop
-        auto staged_walk = [&](uint32_t count, auto&& body) {
-            for (uint32_t t0 = 0; t0 < count; t0 += 4096u) {
-                const uint32_t nt = min(4096u, count - t0);
-                for (uint32_t e = tid; e < nt; e += kThreads)
-                    keys[e] = P[t0 + e];
-                __syncthreads();
-                if (tid == 0) {
-                    bool stop = false;
-                    for (uint32_t e = 0; e < nt && !stop; ++e)
-                        stop = body(keys[e], t0 + e);
-                    s.hi_group = stop ? 1u : 0u;
-                }
-                __syncthreads();
-                if (s.hi_group)
-                    break;
-            }
-        };
-        const int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
-        double want = 0.0, band = 0.0;
-        if (cfg.use_topp) { // sampler.cpp:44-61
-            double total = 0.0;
-            if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
-                total = total_need;
-                band = band_need;
-            } else {
-                double part = 0.0;
-                for (uint32_t i = tid; i < n_list; i += kThreads)
-                    part += (double)__uint_as_float(~(uint32_t)(P[i] >> 32));
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
-                    part += __shfl_xor_sync(0xffffffffu, part, o);
-                if (lane == 0)
-                    s.warp_sum[warp] = part;
-                __syncthreads();
-                for (int i = 0; i < kThreads / 32; ++i)
-                    total += s.warp_sum[i];
-                band = 0x1p-30 * total; // the block-wide sum is not the reference's left-to-right one
-            }
-            want = (double)cfg.top_p * total;
-        }
-        // walk 1: nucleus length, float total, the draft's weight
-        double run = 0.0, prev = 0.0;
-        float total_f = 0.0f, q_draft = 0.0f;
-        uint32_t n_nuc = 0;
-        staged_walk(n_list, [&](unsigned long long key, uint32_t) -> bool {
-            if (cfg.use_topp && !(run < want))
-                return true;
-            const float q = __uint_as_float(~(uint32_t)(key >> 32));
-            prev = run;
-            run += (double)q;
-            total_f = __fadd_rn(total_f, q);
-            if ((int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset == draft)
-                q_draft = q;
-            ++n_nuc;
-            return false;
-        });
-        // walk 2: the draw
-        int32_t tok = -1, acc = 0, last = -1;
-        float prob = 0.0f, last_q = 0.0f, r = 0.0f, walk_total = 0.0f, eps = 0.0f;
-        bool skip_draft = false, first = true;
-        uint32_t picked = 0xffffffffu;
-        if (tid == 0) {
-            if (cfg.use_topp) {
-                if (cfg.need_sum && run < want)
-                    flags |= MK_FLAG_GUARD_BAND;
-                if (n_nuc >= 1 && (fabs(run - want) <= band || (n_nuc >= 2 && fabs(prev - want) <= band)))
-                    flags |= MK_FLAG_GUARD_BAND;
-            }
-            n_nuc = max(n_nuc, 1u);
-            walk_total = total_f;
-            if (a.mode == kModeVerify) {
-                acc = __fmul_rn(u_row, total_f) < q_draft;
-                if (acc) {
-                    tok = draft;
-                    prob = __fdiv_rn(q_draft, total_f);
-                } else {
-                    skip_draft = true;
-                    walk_total = __fsub_rn(total_f, q_draft);
-                }
-            }
-            r = __fmul_rn((a.mode == kModeVerify) ? u2_row : u_row, walk_total);
-            eps = 1e-6f * walk_total;
-            s.n_final = n_nuc;
-            s.nsurv = acc ? 1u : 0u;
-        }
-        __syncthreads();
-        const uint32_t n_fin = s.n_final;
-        if (!s.nsurv)
-            staged_walk(n_fin, [&](unsigned long long key, uint32_t idx) -> bool {
-                const int32_t id = (int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset;
-                if (skip_draft && id == draft)
-                    return false;
-                const float q = __uint_as_float(~(uint32_t)(key >> 32));
-                last = id;
-                last_q = q;
-                if (r < q) {
-                    tok = id;
-                    prob = __fdiv_rn(q, walk_total);
-                    picked = idx;
-                    if ((!first && r < eps) || (idx + 1 < n_fin && __fsub_rn(q, r) < eps))
-                        flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
-                    return true;
-                }
-                r = __fsub_rn(r, q);
-                first = false;
-                return false;
-            });
-        if (tid == 0) {
-            if (tok < 0) { // rounding: the last candidate (sampler.cpp:72)
-                tok = last;
-                prob = __fdiv_rn(last_q, walk_total);
-            }
-            if (a.token) a.token[row] = tok;
-            if (a.prob) a.prob[row] = prob;
-            if (a.flags) a.flags[row] = flags;
-            if (a.n_cand) a.n_cand[row] = n_fin;
-            if (a.accepted) a.accepted[row] = acc;
-            if (a.total_out) a.total_out[row] = total_f;
-            if (a.timing) a.timing[(size_t)row * 64 + 3] = global_ns();
-        }
-        if (a.cand_ids || a.cand_q) {
-            const uint32_t nf = min(n_fin, a.cand_cap);
-            for (uint32_t i = tid; i < nf; i += kThreads) {
-                const unsigned long long key = P[i];
-                if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset;
-                if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + i] = __uint_as_float(~(uint32_t)(key >> 32));
-            }
-        }
-        return;
+        ksrc = P;
+        pre_sorted = true;
     }
-    if (n > (uint32_t)kSortCap)
+    if (!pre_sorted && n > (uint32_t)kSortCap)
         overflow = true;
     if (overflow) {
         if (tid == 0) {
@@ -1393,27 +1306,29 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     const bool cut_k = cfg.top_k > 0 && cfg.top_k < n;       // sampler.cpp:39
     const bool sorted = cut_k || cfg.use_topp;               // else ascending id
-    constexpr bool kOrdFits = sizeof(Smem::counts) + sizeof(Smem::hist) >= kSortCap * sizeof(uint16_t);
     // Ascending id needs no sort: a bitmap of the candidates' columns ranks them, and `ord` lists the candidates'
     // slots by rank. (Vocabularies beyond the bitmap, and lists too short to be worth it, sort by column.)
-    const bool by_rank = kOrdFits && !sorted && V <= kMaxBitmapVocab && n > 64u;
-    static_assert(offsetof(Smem, hist) == offsetof(Smem, counts) + sizeof(Smem::counts), "ord spans counts and hist");
-    uint16_t* const ord = reinterpret_cast<uint16_t*>(s.counts);
-    if (by_rank) {
+    const bool by_rank = !pre_sorted && !sorted && V <= kMaxBitmapVocab && n > 64u;
+    uint32_t* const fbitmap = reinterpret_cast<uint32_t*>(dyn + kOffFinBitmap);
+    uint16_t* const fwpre = reinterpret_cast<uint16_t*>(dyn + kOffFinWpre);
+    uint16_t* const ord = reinterpret_cast<uint16_t*>(dyn + kOffFinOrd);
+    if (pre_sorted) {
+        // ordered above
+    } else if (by_rank) {
         const uint32_t words = (V + 31u) >> 5;
         for (uint32_t w = tid; w < words; w += kThreads)
-            s.bitmap[w] = 0u;
+            fbitmap[w] = 0u;
         __syncthreads();
         for (uint32_t i = tid; i < n; i += kThreads) {
             const uint32_t col = (uint32_t)(keys[i] & 0xffffffffull);
-            atomicOr(&s.bitmap[col >> 5], 1u << (col & 31u));
+            atomicOr(&fbitmap[col >> 5], 1u << (col & 31u));
         }
         __syncthreads();
-        word_ranks(s, words);
+        word_ranks(s, fbitmap, fwpre, words);
         __syncthreads();
         for (uint32_t i = tid; i < n; i += kThreads) {
             const uint32_t col = (uint32_t)(keys[i] & 0xffffffffull);
-            ord[s.wpre[col >> 5] + __popc(s.bitmap[col >> 5] & ((1u << (col & 31u)) - 1u))] = (uint16_t)i;
+            ord[fwpre[col >> 5] + __popc(fbitmap[col >> 5] & ((1u << (col & 31u)) - 1u))] = (uint16_t)i;
         }
         __syncthreads();
     } else {
@@ -1439,7 +1354,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // the r-th candidate of the list in the reference's order
     auto fetch = [&](uint32_t r, float& q, uint32_t& col) {
         if (sorted) {
-            const unsigned long long key = keys[r];
+            const unsigned long long key = ksrc[r];
             q = __uint_as_float(~(uint32_t)(key >> 32));
             col = (uint32_t)(key & 0xffffffffull);
         } else if (by_rank) {
@@ -1470,6 +1385,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         n = cfg.top_k;
     }
     const bool short_list = n <= 128u; // one warp does it all, in the reference's own order, without CTA barriers
+    bool retry = false; // first launch, top_p alone: what was kept does not settle the nucleus; the second pass will
     if (cfg.use_topp && !short_list) {
         // sampler.cpp:44-61: the shortest prefix of the sorted list whose double sum reaches top_p * total. The sums
         // are taken by the whole CTA (each thread a contiguous run of the list, then a scan over threads); their
@@ -1534,10 +1450,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
         __syncthreads();
         const double run = s.warp_sum[0], prev = s.warp_sum[1];
-        if (cfg.need_sum && run < want)
-            flags |= MK_FLAG_GUARD_BAND; // the collected list ended before the nucleus did
-        if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
-            flags |= MK_FLAG_GUARD_BAND;
+        // the collected list ended before the nucleus did, or the decision lies within the margin
+        if ((cfg.need_sum && run < want) ||
+            (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))) {
+            if (cfg.optimistic)
+                retry = true;
+            else
+                flags |= MK_FLAG_GUARD_BAND;
+        }
         n = max(k, 1u);
     }
 
@@ -1582,19 +1502,28 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     }
                 }
             }
-            if (cfg.need_sum && run < want)
-                flags |= MK_FLAG_GUARD_BAND; // the collected list ended before the nucleus did
-            if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
-                flags |= MK_FLAG_GUARD_BAND;
+            if ((cfg.need_sum && run < want) ||
+                (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))) {
+                if (cfg.optimistic)
+                    retry = true;
+                else
+                    flags |= MK_FLAG_GUARD_BAND;
+            }
             n = max(k, 1u);
         }
         float total = 0.0f, q_draft = 0.0f;
         uint32_t draft_idx = 0xffffffffu;
+        float q_next = 0.0f; // the next 32 candidates are fetched while this chain runs (long lists sit in global memory)
+        uint32_t col_next = 0xffffffffu;
+        if (lane < n)
+            fetch(lane, q_next, col_next);
         for (uint32_t base = 0; base < n; base += 32u) {
-            float q = 0.0f;
-            uint32_t col = 0xffffffffu;
-            if (base + lane < n)
-                fetch(base + lane, q, col);
+            const float q = q_next;
+            const uint32_t col = col_next;
+            q_next = 0.0f;
+            col_next = 0xffffffffu;
+            if (base + 32u + lane < n)
+                fetch(base + 32u + lane, q_next, col_next);
             const uint32_t dm = __ballot_sync(full, draft >= 0 && base + lane < n && (int32_t)col + a.id_offset == draft);
             if (dm) {
                 q_draft = __shfl_sync(full, q, __ffs(dm) - 1);
@@ -1638,10 +1567,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 bool found = false;
                 uint32_t hit = 0;
                 float r_hit = 0.0f, q_hit = 0.0f;
+                float qn = (lane < n && lane != skip_idx) ? q_of(lane) : 0.0f;
                 for (uint32_t base = 0; base < n && !found; base += 32u) {
-                    float q = 0.0f; // the skipped draft: weight 0 never wins and changes nothing
-                    if (base + lane < n && base + lane != skip_idx)
-                        q = q_of(base + lane);
+                    const float q = qn; // the skipped draft has weight 0: it never wins and changes nothing
+                    qn = (base + 32u + lane < n && base + 32u + lane != skip_idx) ? q_of(base + 32u + lane) : 0.0f;
                     const int cnt = (int)min(32u, n - base);
 #pragma unroll 8
                     for (int j = 0; j < cnt; ++j) {
@@ -1672,7 +1601,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
         }
         if (lane == 0) {
-            if (a.token) a.token[row] = tok;
+            if (retry)
+                again[0] = 1u; // every output of this row is written again by the second pass
+            if (a.token) a.token[row] = retry ? -1 : tok;
             if (a.prob) a.prob[row] = prob;
             if (a.flags) a.flags[row] = flags;
             if (a.n_cand) a.n_cand[row] = n;
@@ -1698,7 +1629,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 
 size_t row_kernel_smem_bytes()
 {
-    return sizeof(Smem);
+    return kSmemBytes;
 }
 
 cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream_t stream)
@@ -1709,15 +1640,32 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     if (e != cudaSuccess)
         return e;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(row_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+        e = cudaFuncSetAttribute(row_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess)
             return e;
         configured[dev] = true;
     }
     if (batch == 0)
         return cudaSuccess;
-    row_pipeline_kernel<<<batch, kThreads, sizeof(Smem), stream>>>(a);
-    return cudaGetLastError();
+    RowKernelArgs first = a;
+    first.pass = 0;
+    row_pipeline_kernel<<<batch, kThreads, kSmemBytes, stream>>>(first);
+    e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return e;
+    // top_p alone (make_cfg: need_sum): rows whose nucleus the first launch could not settle are streamed again
+    // with the loose bound. With per-row parameters on the device any row may be one; CTAs of other rows return at once.
+    const mk_sampling_params& p = a.params;
+    const float minp_eff = (1.0f < p.min_p) ? 1.0f : p.min_p;
+    const bool host_need_sum = !(p.temperature <= 0.0f) && p.top_p < 1.0f && !(minp_eff > 0.0f) &&
+                               !(p.top_k > 0 && p.top_k < a.n_vocab);
+    if (a.mode != kModeVpLocal && kNucleusGuess < a.n_vocab && (a.params_dev || host_need_sum)) {
+        RowKernelArgs second = a;
+        second.pass = 1;
+        row_pipeline_kernel<<<batch, kThreads, kSmemBytes, stream>>>(second);
+        e = cudaGetLastError();
+    }
+    return e;
 }
 
 // ---- test hook --------------------------------------------------------------------------------------------------

@@ -48,13 +48,17 @@ struct RowKernelArgs {
     void* vp_records;
     uint32_t vp_k;
     // scratch owned by the handle
-    uint32_t* scratch;     // [batch][4*scratch_cap] words: raw candidates (logit bits, column), then a sort buffer / a float per column
+    uint32_t* scratch;     // [batch][row_scratch_words(scratch_cap)]: raw candidates (logit bits, column), then a sort buffer / a float per column
     uint32_t scratch_cap;
-    unsigned long long* timing; // optional [batch][64] ns timestamps: start, set-up done, streaming done, end, set-up steps
-    uint32_t dbg;          // profiling switches (0 in production)
+    unsigned long long* timing; // optional [batch][64] ns timestamps (slots: see mk_debug_set_timing)
     int mode;
+    int pass;              // 0: first launch; 1: second pass, only the rows that asked for it (set by launch_row_kernel)
     int use_bulk_copy;     // 1: TMA bulk staging (aligned rows); 0: plain loads
 };
+
+// Words of handle scratch per row: 4 per column of capacity, then 4 of per-row state (word 0: the row asks for the
+// second pass).
+__host__ __device__ inline size_t row_scratch_words(uint32_t cap) { return 4ull * cap + 4ull; }
 
 size_t row_kernel_smem_bytes();
 cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream_t stream);
