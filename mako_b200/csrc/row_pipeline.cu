@@ -65,6 +65,7 @@ constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) 
 #define MK_BINS 2048
 #define MK_BINSHIFT 21
 #endif
+constexpr uint32_t kBarSort = 3;         // named barrier of the sorting warps
 constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates kept
 constexpr int kBins = MK_BINS;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = MK_BINSHIFT;
@@ -279,25 +280,32 @@ __device__ __forceinline__ void word_ranks(Smem& s, const uint32_t* bitmap, uint
         s.n_distinct = before; // every word lies at or before the last thread's run
 }
 
-// Bitonic sort of n2 (power of two) 64-bit keys in shared memory by the whole CTA.
+// Bitonic sort of n2 (power of two) 64-bit keys in shared memory. Called by the whole CTA; only as many warps as
+// have a compare-exchange to do per step take part (a short list is sorted by a few warps over a cheap named barrier
+// instead of by 352 threads over the CTA's), the others wait at the end.
 __device__ void block_sort(unsigned long long* keys, uint32_t n2)
 {
-    for (uint32_t k = 2; k <= n2; k <<= 1) {
-        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-            for (uint32_t i = threadIdx.x; i < n2; i += kThreads) {
-                const uint32_t l = i ^ j;
-                if (l > i) {
+    const uint32_t nthr = min((uint32_t)kThreads, max(32u, ((n2 >> 1) + 31u) & ~31u));
+    if (threadIdx.x < nthr) {
+        for (uint32_t k = 2; k <= n2; k <<= 1) {
+            for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+                for (uint32_t c = threadIdx.x; c < (n2 >> 1); c += nthr) {
+                    // the c-th pair of this step: i has bit j clear
+                    const uint32_t i = ((c & ~(j - 1u)) << 1) | (c & (j - 1u)), l = i | j;
                     const unsigned long long a = keys[i], b = keys[l];
-                    const bool up = (i & k) == 0;
-                    if ((a > b) == up) {
+                    if ((a > b) == ((i & k) == 0)) {
                         keys[i] = b;
                         keys[l] = a;
                     }
                 }
+                if (nthr == 32u)
+                    __syncwarp();
+                else
+                    named_barrier(kBarSort, nthr);
             }
-            __syncthreads();
         }
     }
+    __syncthreads();
 }
 
 // One pass of a merge sort over n 64-bit keys in global memory: runs of w sorted keys in `src` are merged pairwise
