@@ -32,6 +32,7 @@
 #include "ptx.cuh"
 
 #include <cfloat>
+#include <type_traits>
 
 #ifndef MK_TILE
 #define MK_TILE 4096
@@ -704,159 +705,178 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         const bool collect = !cfg.greedy || a.mode == kModeVpLocal;
         const bool sum_all = a.mode == kModeVpLocal;
         float warp_pub = ninf;
-        uint32_t mw_next[kVec];
-#pragma unroll
-        for (int j = 0; j < kVec; ++j) {
-            const uint32_t i0 = j * 1024 + rt * 4;
-            mw_next[j] = mrow ? ((i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u) : 0xffffffffu;
-        }
-        uint32_t st = 0, k = 0;
-        for (uint32_t t = 0; t < n_tiles; ++t, ++st) {
-            if (st == n_stages) {
-                st = 0;
-                ++k;
-            }
-            const uint32_t base = t * kTile;
-            uint32_t mw[kVec]; // this tile's mask words were requested a tile ago
-#pragma unroll
-            for (int j = 0; j < kVec; ++j)
-                mw[j] = mw_next[j];
-            if (mrow) {
-#pragma unroll
-                for (int j = 0; j < kVec; ++j) {
-                    const uint32_t i0 = base + kTile + j * 1024 + rt * 4;
-                    mw_next[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
-                }
-            }
-            if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
-                atomicExch(&s.abort_flag, 1u); // keep walking: the named barriers below must stay matched
-            float w[kEl];
-            const float4* tp4 = reinterpret_cast<const float4*>(ring + st * kTile);
+        // The loop over the tiles is compiled once per combination of {mask, top_k histogram, streamed sum}: a row
+        // runs the variant that holds only its own work. (One loop with all three as run-time branches costs the
+        // common penalised row 12 % of its launch time in instruction fetch.)
+        auto read_tiles = [&](auto has_mask, auto has_hist, auto has_sum) {
+            constexpr bool kMask = decltype(has_mask)::value, kHist = decltype(has_hist)::value,
+                           kSum = decltype(has_sum)::value;
+            uint32_t mw_next[kVec];
 #pragma unroll
             for (int j = 0; j < kVec; ++j) {
-                const float4 v = tp4[j * 256 + rt];
-                w[4 * j + 0] = v.x;
-                w[4 * j + 1] = v.y;
-                w[4 * j + 2] = v.z;
-                w[4 * j + 3] = v.w;
+                const uint32_t i0 = j * 1024 + rt * 4;
+                mw_next[j] = kMask ? ((i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u) : 0xffffffffu;
             }
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&s.empty[st]);
-
-            if (mrow) {
-#pragma unroll
-                for (int j = 0; j < kVec; ++j) {
-                    const uint32_t bits = mw[j] >> ((rt * 4) & 31);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (!((bits >> c) & 1u))
-                            w[4 * j + c] = ninf;
+            uint32_t st = 0, k = 0;
+            for (uint32_t t = 0; t < n_tiles; ++t, ++st) {
+                if (st == n_stages) {
+                    st = 0;
+                    ++k;
                 }
-            }
-            if (base + kTile > V) {
+                const uint32_t base = t * kTile;
+                uint32_t mw[kVec]; // this tile's mask words were requested a tile ago
 #pragma unroll
                 for (int j = 0; j < kVec; ++j)
+                    mw[j] = mw_next[j];
+                if constexpr (kMask) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (base + j * 1024 + rt * 4 + c >= V)
-                            w[4 * j + c] = ninf;
-            }
-            if (t == 0 && rt == 0 && w[0] != w[0])
-                s.nan0 = 1;
-
-            float tm = ninf;
-#pragma unroll
-            for (int e = 0; e < kEl; ++e)
-                tm = fmaxf(tm, w[e]);
-            const float old_best = best;
-            if (tm > best) {
-                best = tm;
-#pragma unroll
-                for (int e = kEl - 1; e >= 0; --e)
-                    if (w[e] == tm)
-                        best_col = (int32_t)(base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-            }
-            if (__any_sync(0xffffffffu, tm > warp_pub)) {
-                const float wm = warp_max(tm);
-                if (wm > warp_pub) {
-                    warp_pub = wm;
-                    if (lane == 0)
-                        atomicMax(&s.m_key, order_key(wm));
+                    for (int j = 0; j < kVec; ++j) {
+                        const uint32_t i0 = base + kTile + j * 1024 + rt * 4;
+                        mw_next[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
+                    }
                 }
-            }
-            float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
-            if (cfg.hist_mode) {
-                // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
-                // where the count from the top reaches k bounds the k-th largest from below.
-                thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
-                if (tm >= thr) {
-                    // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
-                    // valid one too (bounds only rise), and one pass over the 16 elements costs half of two
-                    uint32_t top_bin = 0;
+                if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
+                    atomicExch(&s.abort_flag, 1u); // keep walking: the named barriers below must stay matched
+                float w[kEl];
+                const float4* tp4 = reinterpret_cast<const float4*>(ring + st * kTile);
+#pragma unroll
+                for (int j = 0; j < kVec; ++j) {
+                    const float4 v = tp4[j * 256 + rt];
+                    w[4 * j + 0] = v.x;
+                    w[4 * j + 1] = v.y;
+                    w[4 * j + 2] = v.z;
+                    w[4 * j + 3] = v.w;
+                }
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&s.empty[st]);
+
+                if constexpr (kMask) {
+#pragma unroll
+                    for (int j = 0; j < kVec; ++j) {
+                        const uint32_t bits = mw[j] >> ((rt * 4) & 31);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (!((bits >> c) & 1u))
+                                w[4 * j + c] = ninf;
+                    }
+                }
+                if (base + kTile > V) {
+#pragma unroll
+                    for (int j = 0; j < kVec; ++j)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (base + j * 1024 + rt * 4 + c >= V)
+                                w[4 * j + c] = ninf;
+                }
+                if (t == 0 && rt == 0 && w[0] != w[0])
+                    s.nan0 = 1;
+
+                float tm = ninf;
+#pragma unroll
+                for (int e = 0; e < kEl; ++e)
+                    tm = fmaxf(tm, w[e]);
+                const float old_best = best;
+                if (tm > best) {
+                    best = tm;
+#pragma unroll
+                    for (int e = kEl - 1; e >= 0; --e)
+                        if (w[e] == tm)
+                            best_col = (int32_t)(base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                }
+                if (__any_sync(0xffffffffu, tm > warp_pub)) {
+                    const float wm = warp_max(tm);
+                    if (wm > warp_pub) {
+                        warp_pub = wm;
+                        if (lane == 0)
+                            atomicMax(&s.m_key, order_key(wm));
+                    }
+                }
+                float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
+                if constexpr (kHist) {
+                    // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
+                    // where the count from the top reaches k bounds the k-th largest from below.
+                    thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
+                    if (tm >= thr) {
+                        // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
+                        // valid one too (bounds only rise), and one pass over the 16 elements costs half of two
+                        uint32_t top_bin = 0;
+#pragma unroll
+                        for (int e = 0; e < kEl; ++e)
+                            if (w[e] >= thr) {
+                                const uint32_t bin = order_key(w[e]) >> kBinShift;
+                                atomicAdd(&hist[bin], 1u);
+                                top_bin = max(top_bin, bin);
+                                if (collect) {
+                                    const uint32_t slot = atomicAdd(&s.ncand, 1u);
+                                    if (slot < a.scratch_cap)
+                                        scratch[slot] = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                                }
+                            }
+                        if ((top_bin >> 5) > *(volatile uint32_t*)&s.hi_group)
+                            atomicMax(&s.hi_group, top_bin >> 5);
+                    }
+                    // One reader warp per tile rescans the histogram and raises the bound; nobody waits for it. Counts
+                    // only grow and every count is an element at or above its bin's edge, so a bound read from a
+                    // histogram that other warps are still adding to has its k elements all the same.
+                    __syncwarp();
+                    if (rwarp == (t % (kReaders / 32))) {
+                        uint32_t cum = 0;
+                        int found = -1;
+                        for (int g = (int)*(volatile uint32_t*)&s.hi_group; g >= 0 && found < 0; --g) {
+                            const uint32_t cbin = ((volatile uint32_t*)hist)[g * 32 + lane];
+                            uint32_t suf = cbin; // suffix sum over lanes >= lane
+#pragma unroll
+                            for (int o = 1; o < 32; o <<= 1) {
+                                const uint32_t y = __shfl_down_sync(0xffffffffu, suf, o);
+                                if ((int)lane + o < 32)
+                                    suf += y;
+                            }
+                            const uint32_t hit = __ballot_sync(0xffffffffu, cum + suf >= cfg.hist_k);
+                            if (hit)
+                                found = g * 32 + (31 - __clz(hit));
+                            cum += __shfl_sync(0xffffffffu, suf, 0);
+                        }
+                        // the lowest key of a bin is its smallest float; bin 0 (NaN keys) is never a bound
+                        if (lane == 0 && found > 0)
+                            atomicMax(&s.thr_topk_key, (uint32_t)found << kBinShift);
+                    }
+                }
+                if (kSum && best > ninf) {
+                    // Approximate weight of what is NOT collected (`thr` is the bound the collection used; a shard record
+                    // sums everything): the collected
+                    // elements get exact weights in the finish, so only the far tail carries the approximation.
+                    if (best > old_best)
+                        sum_acc *= (double)exp2f((old_best - best) * c2);
+                    float p = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < kEl; ++e)
+                        p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
+                    sum_acc += (double)p;
+                }
+                if (!kHist && collect && tm >= thr) {
 #pragma unroll
                     for (int e = 0; e < kEl; ++e)
                         if (w[e] >= thr) {
-                            const uint32_t bin = order_key(w[e]) >> kBinShift;
-                            atomicAdd(&hist[bin], 1u);
-                            top_bin = max(top_bin, bin);
-                            if (collect) {
-                                const uint32_t slot = atomicAdd(&s.ncand, 1u);
-                                if (slot < a.scratch_cap)
-                                    scratch[slot] = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-                            }
+                            const uint32_t slot = atomicAdd(&s.ncand, 1u);
+                            const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                            if (slot < a.scratch_cap)
+                                scratch[slot] = c;
                         }
-                    if ((top_bin >> 5) > *(volatile uint32_t*)&s.hi_group)
-                        atomicMax(&s.hi_group, top_bin >> 5);
-                }
-                // One reader warp per tile rescans the histogram and raises the bound; nobody waits for it. Counts
-                // only grow and every count is an element at or above its bin's edge, so a bound read from a
-                // histogram that other warps are still adding to has its k elements all the same.
-                __syncwarp();
-                if (rwarp == (t % (kReaders / 32))) {
-                    uint32_t cum = 0;
-                    int found = -1;
-                    for (int g = (int)*(volatile uint32_t*)&s.hi_group; g >= 0 && found < 0; --g) {
-                        const uint32_t cbin = ((volatile uint32_t*)hist)[g * 32 + lane];
-                        uint32_t suf = cbin; // suffix sum over lanes >= lane
-#pragma unroll
-                        for (int o = 1; o < 32; o <<= 1) {
-                            const uint32_t y = __shfl_down_sync(0xffffffffu, suf, o);
-                            if ((int)lane + o < 32)
-                                suf += y;
-                        }
-                        const uint32_t hit = __ballot_sync(0xffffffffu, cum + suf >= cfg.hist_k);
-                        if (hit)
-                            found = g * 32 + (31 - __clz(hit));
-                        cum += __shfl_sync(0xffffffffu, suf, 0);
-                    }
-                    // the lowest key of a bin is its smallest float; bin 0 (NaN keys) is never a bound
-                    if (lane == 0 && found > 0)
-                        atomicMax(&s.thr_topk_key, (uint32_t)found << kBinShift);
                 }
             }
-            if (cfg.need_sum && best > ninf) {
-                // Approximate weight of what is NOT collected (`thr` is the bound the collection used; a shard record
-                // sums everything): the collected
-                // elements get exact weights in the finish, so only the far tail carries the approximation.
-                if (best > old_best)
-                    sum_acc *= (double)exp2f((old_best - best) * c2);
-                float p = 0.0f;
-#pragma unroll
-                for (int e = 0; e < kEl; ++e)
-                    p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
-                sum_acc += (double)p;
-            }
-            if (collect && !cfg.hist_mode && tm >= thr) {
-#pragma unroll
-                for (int e = 0; e < kEl; ++e)
-                    if (w[e] >= thr) {
-                        const uint32_t slot = atomicAdd(&s.ncand, 1u);
-                        const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-                        if (slot < a.scratch_cap)
-                            scratch[slot] = c;
-                    }
-            }
+        };
+        using T = std::true_type;
+        using F = std::false_type;
+        switch ((mrow ? 1 : 0) | (cfg.hist_mode ? 2 : 0) | (cfg.need_sum ? 4 : 0)) {
+        case 0: read_tiles(F{}, F{}, F{}); break;
+        case 1: read_tiles(T{}, F{}, F{}); break;
+        case 2: read_tiles(F{}, T{}, F{}); break;
+        case 3: read_tiles(T{}, T{}, F{}); break;
+        case 4: read_tiles(F{}, F{}, T{}); break;
+        case 5: read_tiles(T{}, F{}, T{}); break;
+        case 6: read_tiles(F{}, T{}, T{}); break;
+        default: read_tiles(T{}, T{}, T{}); break;
         }
         if (best_col >= 0)
             atomicMax(&s.best_key,
