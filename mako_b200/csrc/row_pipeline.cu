@@ -705,9 +705,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         const bool collect = !cfg.greedy || a.mode == kModeVpLocal;
         const bool sum_all = a.mode == kModeVpLocal;
         float warp_pub = ninf;
-        // The loop over the tiles is compiled once per combination of {mask, top_k histogram, streamed sum}: a row
-        // runs the variant that holds only its own work. (One loop with all three as run-time branches costs the
-        // common penalised row 12 % of its launch time in instruction fetch.)
+        // The loop over the tiles is compiled four times, with the mask, the top_k histogram and the streamed sum
+        // compiled in or out: a row runs a variant that holds little beyond its own work. (One loop with all
+        // three as run-time branches costs the common penalised row 12 % of its launch time, and all eight
+        // combinations cost it 3 % again: the size of the code matters, executed or not.)
         auto read_tiles = [&](auto has_mask, auto has_hist, auto has_sum) {
             constexpr bool kMask = decltype(has_mask)::value, kHist = decltype(has_hist)::value,
                            kSum = decltype(has_sum)::value;
@@ -715,7 +716,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 #pragma unroll
             for (int j = 0; j < kVec; ++j) {
                 const uint32_t i0 = j * 1024 + rt * 4;
-                mw_next[j] = kMask ? ((i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u) : 0xffffffffu;
+                mw_next[j] = (kMask && mrow) ? ((i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u) : 0xffffffffu;
             }
             uint32_t st = 0, k = 0;
             for (uint32_t t = 0; t < n_tiles; ++t, ++st) {
@@ -728,7 +729,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 #pragma unroll
                 for (int j = 0; j < kVec; ++j)
                     mw[j] = mw_next[j];
-                if constexpr (kMask) {
+                if (kMask && mrow) {
 #pragma unroll
                     for (int j = 0; j < kVec; ++j) {
                         const uint32_t i0 = base + kTile + j * 1024 + rt * 4;
@@ -751,7 +752,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 if (lane == 0)
                     mbar_arrive(&s.empty[st]);
 
-                if constexpr (kMask) {
+                if (kMask && mrow) {
 #pragma unroll
                     for (int j = 0; j < kVec; ++j) {
                         const uint32_t bits = mw[j] >> ((rt * 4) & 31);
@@ -793,7 +794,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     }
                 }
                 float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
-                if constexpr (kHist) {
+                if (kHist && cfg.hist_mode) {
                     // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
                     // where the count from the top reaches k bounds the k-th largest from below.
                     thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
@@ -842,7 +843,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                             atomicMax(&s.thr_topk_key, (uint32_t)found << kBinShift);
                     }
                 }
-                if (kSum && best > ninf) {
+                if (kSum && cfg.need_sum && best > ninf) {
                     // Approximate weight of what is NOT collected (`thr` is the bound the collection used; a shard record
                     // sums everything): the collected
                     // elements get exact weights in the finish, so only the far tail carries the approximation.
@@ -854,7 +855,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
                     sum_acc += (double)p;
                 }
-                if (!kHist && collect && tm >= thr) {
+                if (!(kHist && cfg.hist_mode) && collect && tm >= thr) {
 #pragma unroll
                     for (int e = 0; e < kEl; ++e)
                         if (w[e] >= thr) {
@@ -868,16 +869,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         };
         using T = std::true_type;
         using F = std::false_type;
-        switch ((mrow ? 1 : 0) | (cfg.hist_mode ? 2 : 0) | (cfg.need_sum ? 4 : 0)) {
-        case 0: read_tiles(F{}, F{}, F{}); break;
-        case 1: read_tiles(T{}, F{}, F{}); break;
-        case 2: read_tiles(F{}, T{}, F{}); break;
-        case 3: read_tiles(T{}, T{}, F{}); break;
-        case 4: read_tiles(F{}, F{}, T{}); break;
-        case 5: read_tiles(T{}, F{}, T{}); break;
-        case 6: read_tiles(F{}, T{}, T{}); break;
-        default: read_tiles(T{}, T{}, T{}); break;
-        }
+        if (!mrow && !cfg.hist_mode && !cfg.need_sum)
+            read_tiles(F{}, F{}, F{}); // penalties, min_p, greedy: nothing but maximum and bound
+        else if (!mrow && !cfg.need_sum)
+            read_tiles(F{}, T{}, F{}); // top_k
+        else if (!mrow)
+            read_tiles(F{}, T{}, T{}); // top_p alone (with its first-launch histogram), shard records
+        else
+            read_tiles(T{}, T{}, T{}); // masked rows: everything, chosen at run time
         if (best_col >= 0)
             atomicMax(&s.best_key,
                       ((unsigned long long)order_key(best) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)best_col));
