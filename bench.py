@@ -61,6 +61,14 @@ def measured_hbm_peak():
         return 6650.0, "fallback"
 
 
+def launches_per_step(params, n_vocab: int) -> int:
+    """Row-kernel launches one sample call makes: top_p alone (no min_p, no top_k) is followed by the second pass
+    that streams again the rows whose nucleus the first launch could not settle (other CTAs return at once)."""
+    top_p_alone = (params.temperature > 0 and params.top_p < 1.0 and not min(params.min_p, 1.0) > 0
+                   and not 0 < params.top_k < n_vocab)
+    return 2 if top_p_alone and n_vocab > 256 else 1
+
+
 def committed_traffic(workload_key: str):
     """DRAM bytes per launch of the row kernel from the committed ncu capture, if one exists for this workload."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
@@ -369,7 +377,7 @@ def main() -> None:
                          "kernel": "row_pipeline_kernel"},
             "e2e": {"value": world * b * e2e_steps / e2e_sec, "unit": "rows/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 12 * b, "steps": e2e_steps},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * launches_per_step(params, v),
             "one_batch_in_flight": None if ms_serial is None else {
                 "ms_per_step": ms_serial / args.steps, "value": b * args.steps / (ms_serial / 1e3),
                 "roofline_frac": rb * b / (ms_serial / args.steps / 1e3) / 1e9 / peak},
