@@ -164,3 +164,27 @@ def test_flat_rows_keep_long_sorted_lists(gpu_sampler_factory, ref, params):
     tok, acc = vr.token.cpu().numpy(), vr.accepted.cpu().numpy()
     for i in range(b):
         assert (tok[i], bool(acc[i])) == ref.verify(params, rows[i], int(draft[i]), u[i], u2[i]), f"row {i}"
+
+
+def test_second_pass_only_for_rows_that_ask(gpu_sampler_factory, ref):
+    """top_p alone: the first launch keeps the 256 largest elements per row; rows whose nucleus is longer stream a
+    second time. Flat and peaked rows share a batch, with histories and a mask, and the same handle is then used for
+    a batch in which no row asks for the second pass: marks left by one call must not leak into the next."""
+    v, b, cap = 50021, 8, 4096
+    inp = Inputs(171, b, v, n_history=300, with_mask=True, mask_fraction=0.6)
+    rng = np.random.default_rng(5)
+    for i in (1, 4, 6):                          # flat rows: nuclei of thousands
+        inp.logits[i, :v] = rng.normal(0, 0.5, size=v).astype(np.float32)
+    p = SamplingParams(temperature=0.9, top_p=0.92, repetition_penalty=1.2, presence_penalty=0.2)
+    g = inp.to_gpu()
+    s = gpu_sampler_factory(v, b, cap)
+    for _ in range(2):
+        res = s.sample(g["logits"], p, g["u"], **g["kw"])
+        want = oracle_sample_rows(ref, p, inp, cap=cap)
+        compare_sample(res, want, cap=cap)
+    n = [w["n_cand"] for w in want]
+    assert max(n) > 256 and min(n) <= 256        # both kinds of row are present
+    inp2 = Inputs(172, b, v, n_history=300)
+    g2 = inp2.to_gpu()
+    res = s.sample(g2["logits"], p, g2["u"], **g2["kw"])
+    compare_sample(res, oracle_sample_rows(ref, p, inp2, cap=cap), cap=cap)
