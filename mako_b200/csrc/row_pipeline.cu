@@ -366,6 +366,133 @@ __device__ void merge_pass(const unsigned long long* src, unsigned long long* ds
     }
 }
 
+// top_p alone, a long collected list: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was
+// not collected belongs to that tail; collected elements can join it from the bottom for as long as the tail stays
+// within the budget. Approximate weights decide the cut (with margins) and raise s.thr_topk_key; the nucleus itself
+// is then computed from exact weights, and a cut that turns out too tight is reported. Whole CTA. (Out of line, like
+// the other steps few rows need: what the common row runs stays short and contiguous.)
+__device__ __noinline__ void mass_cut(Smem& s, float* fh, const uint2* scratch, uint32_t n_raw, float thr_final, float m,
+                                      float inv_t, float top_p, double total_approx)
+{
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+        for (uint32_t i = tid; i < kBins; i += kThreads)
+        fh[i] = 0.0f;
+    if (tid == 0)
+        s.warp_sum[0] = s.warp_sum[1] = 0.0;
+    __syncthreads();
+    const float c2 = inv_t * 1.4426950408889634f;
+    double mine = 0.0, low = 0.0;
+    for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
+        float wv[4]; // four loads in flight
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = i0 + (uint32_t)k * kThreads;
+            wv[k] = (i < n_raw) ? __uint_as_float(scratch[i].x) : -__int_as_float(0x7f800000);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float w = wv[k];
+            const float qa = exp2f((w - m) * c2); // 0 for the filler
+            if (w >= thr_final) {
+                atomicAdd(&fh[order_key(w) >> kBinShift], qa);
+                mine += (double)qa;
+            } else {
+                low += (double)qa;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mine += __shfl_xor_sync(0xffffffffu, mine, o);
+        low += __shfl_xor_sync(0xffffffffu, low, o);
+    }
+    if (lane == 0) {
+        atomicAdd(&s.warp_sum[0], mine);
+        atomicAdd(&s.warp_sum[1], low);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const double collected = s.warp_sum[0];
+        const double outside = total_approx + s.warp_sum[1]; // never collected, or below the final bound
+        const double total_est = collected + outside;
+        const double budget = (1.0 - (double)top_p) * total_est * 0.999 - (outside + 1e-5 * total_est);
+        double cum = 0.0;
+        int cut = 0; // elements in bins below `cut` may be dropped
+        bool stop = false;
+        for (int g = 0; g < kBins / 32 && !stop; ++g) {
+            const float v = fh[g * 32 + lane];
+            double pre = (double)v; // inclusive prefix over lanes
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double y = __shfl_up_sync(0xffffffffu, pre, o);
+                if ((int)lane >= o)
+                    pre += y;
+            }
+            const uint32_t okm = __ballot_sync(0xffffffffu, cum + pre <= budget);
+            if (okm == 0xffffffffu) {
+                cut = (g + 1) * 32;
+                cum += __shfl_sync(0xffffffffu, pre, 31);
+            } else {
+                cut = g * 32 + __ffs(~okm) - 1; // first bin that no longer fits
+                stop = true;
+            }
+        }
+        if (lane == 0 && budget > 0.0 && cut > 0 && cut < kBins) {
+            const float edge = key_to_float((uint32_t)cut << kBinShift);
+            if (edge == edge)
+                s.thr_topk_key = max(s.thr_topk_key, (uint32_t)cut << kBinShift);
+        }
+    }
+    __syncthreads();
+}
+
+// More candidates than the shared-memory sort holds, in an order that matters: the survivors (exact weight, min_p) are
+// compacted into the second half of the row's scratch as sort keys, sorted as kSortCap-key runs in shared memory,
+// then merged pairwise between the two halves. Returns where the sorted list of n keys ends up. Whole CTA.
+__device__ __noinline__ const unsigned long long* long_sort(Smem& s, unsigned long long* keys, uint2* scratch, uint32_t cap,
+                                                            uint32_t n_raw, uint32_t n, float thr2, float m, float inv_t,
+                                                            float minp_eff)
+{
+    const uint32_t tid = threadIdx.x;
+    unsigned long long* KA = reinterpret_cast<unsigned long long*>(scratch) + cap; // second half
+    unsigned long long* KB = reinterpret_cast<unsigned long long*>(scratch);                 // over the raw list
+    if (tid == 0)
+        s.nsurv = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < n_raw; i += kThreads) { // survivors, compacted, as sort keys
+        const uint2 c = scratch[i];
+        if (__uint_as_float(c.x) >= thr2) {
+            const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), inv_t));
+            if (q >= minp_eff && q > 0.0f)
+                KA[atomicAdd(&s.nsurv, 1u)] = pack_by_weight(q, c.y);
+        }
+    }
+    __syncthreads();
+    for (uint32_t r0 = 0; r0 < n; r0 += (uint32_t)kSortCap) {
+        for (uint32_t i = tid; i < (uint32_t)kSortCap; i += kThreads)
+            keys[i] = (r0 + i < n) ? KA[r0 + i] : ~0ull;
+        __syncthreads();
+        block_sort(keys, (uint32_t)kSortCap);
+        for (uint32_t i = tid; i < (uint32_t)kSortCap; i += kThreads)
+            if (r0 + i < n)
+                KA[r0 + i] = keys[i];
+        __syncthreads();
+    }
+    const unsigned long long* P = KA;
+    {
+        unsigned long long *src = KA, *dst = KB;
+        for (uint32_t w = (uint32_t)kSortCap; w < n; w <<= 1) {
+            merge_pass(src, dst, n, w);
+            __syncthreads();
+            unsigned long long* t = src;
+            src = dst;
+            dst = t;
+        }
+        P = src;
+    }
+    return P;
+}
+
 } // namespace
 
 __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKernelArgs a)
@@ -1009,80 +1136,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // Elements collected while the running maximum was still low are dropped by the final bound first.
         float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         if (cfg.need_sum && n_raw > 4096u) {
-            // top_p alone: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was not
-            // collected belongs to that tail; collected elements can join it from the bottom for as long as the
-            // tail stays within the budget. Approximate weights decide the cut (with margins); the nucleus itself
-            // is then computed from exact weights, and a cut that turns out too tight is reported.
-            float* fh = reinterpret_cast<float*>(dyn + kOffFinBitmap);
-            for (uint32_t i = tid; i < kBins; i += kThreads)
-                fh[i] = 0.0f;
-            if (tid == 0)
-                s.warp_sum[0] = s.warp_sum[1] = 0.0;
-            __syncthreads();
-            const float c2 = cfg.inv_t * 1.4426950408889634f;
-            double mine = 0.0, low = 0.0;
-            for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
-                float wv[4]; // four loads in flight
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t i = i0 + (uint32_t)k * kThreads;
-                    wv[k] = (i < n_raw) ? __uint_as_float(scratch[i].x) : -__int_as_float(0x7f800000);
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float w = wv[k];
-                    const float qa = exp2f((w - m) * c2); // 0 for the filler
-                    if (w >= thr_final) {
-                        atomicAdd(&fh[order_key(w) >> kBinShift], qa);
-                        mine += (double)qa;
-                    } else {
-                        low += (double)qa;
-                    }
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                mine += __shfl_xor_sync(0xffffffffu, mine, o);
-                low += __shfl_xor_sync(0xffffffffu, low, o);
-            }
-            if (lane == 0) {
-                atomicAdd(&s.warp_sum[0], mine);
-                atomicAdd(&s.warp_sum[1], low);
-            }
-            __syncthreads();
-            if (warp == 0) {
-                const double collected = s.warp_sum[0];
-                const double outside = total_approx + s.warp_sum[1]; // never collected, or below the final bound
-                const double total_est = collected + outside;
-                const double budget = (1.0 - (double)cfg.top_p) * total_est * 0.999 - (outside + 1e-5 * total_est);
-                double cum = 0.0;
-                int cut = 0; // elements in bins below `cut` may be dropped
-                bool stop = false;
-                for (int g = 0; g < kBins / 32 && !stop; ++g) {
-                    const float v = fh[g * 32 + lane];
-                    double pre = (double)v; // inclusive prefix over lanes
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const double y = __shfl_up_sync(0xffffffffu, pre, o);
-                        if ((int)lane >= o)
-                            pre += y;
-                    }
-                    const uint32_t okm = __ballot_sync(0xffffffffu, cum + pre <= budget);
-                    if (okm == 0xffffffffu) {
-                        cut = (g + 1) * 32;
-                        cum += __shfl_sync(0xffffffffu, pre, 31);
-                    } else {
-                        cut = g * 32 + __ffs(~okm) - 1; // first bin that no longer fits
-                        stop = true;
-                    }
-                }
-                if (lane == 0 && budget > 0.0 && cut > 0 && cut < kBins) {
-                    const float edge = key_to_float((uint32_t)cut << kBinShift);
-                    if (edge == edge)
-                        s.thr_topk_key = max(s.thr_topk_key, (uint32_t)cut << kBinShift);
-                }
-            }
-            __syncthreads();
+            mass_cut(s, reinterpret_cast<float*>(dyn + kOffFinBitmap), scratch, n_raw, thr_final, m, cfg.inv_t, cfg.top_p,
+                     total_approx);
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
         }
         double exact = 0.0;
@@ -1271,43 +1326,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // returned above): a flat row under top_p, or a very large top_k. The candidates are sorted in global
         // memory — 8192-key runs in shared memory, then merge passes between the two halves of the row's scratch —
         // and the steps below read the list from there.
-        unsigned long long* KA = reinterpret_cast<unsigned long long*>(scratch) + a.scratch_cap; // second half
-        unsigned long long* KB = reinterpret_cast<unsigned long long*>(scratch);                 // over the raw list
-        const float thr2 = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
-        if (tid == 0)
-            s.nsurv = 0;
-        __syncthreads();
-        for (uint32_t i = tid; i < n_raw; i += kThreads) { // survivors, compacted, as sort keys
-            const uint2 c = scratch[i];
-            if (__uint_as_float(c.x) >= thr2) {
-                const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
-                if (q >= cfg.minp_eff && q > 0.0f)
-                    KA[atomicAdd(&s.nsurv, 1u)] = pack_by_weight(q, c.y);
-            }
-        }
-        __syncthreads();
-        for (uint32_t r0 = 0; r0 < n; r0 += (uint32_t)kSortCap) {
-            for (uint32_t i = tid; i < (uint32_t)kSortCap; i += kThreads)
-                keys[i] = (r0 + i < n) ? KA[r0 + i] : ~0ull;
-            __syncthreads();
-            block_sort(keys, (uint32_t)kSortCap);
-            for (uint32_t i = tid; i < (uint32_t)kSortCap; i += kThreads)
-                if (r0 + i < n)
-                    KA[r0 + i] = keys[i];
-            __syncthreads();
-        }
-        const unsigned long long* P = KA;
-        {
-            unsigned long long *src = KA, *dst = KB;
-            for (uint32_t w = (uint32_t)kSortCap; w < n; w <<= 1) {
-                merge_pass(src, dst, n, w);
-                __syncthreads();
-                unsigned long long* t = src;
-                src = dst;
-                dst = t;
-            }
-            P = src;
-        }
+        const unsigned long long* P = long_sort(s, keys, scratch, a.scratch_cap, n_raw, n,
+                                                fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key)), m, cfg.inv_t,
+                                                cfg.minp_eff);
         ksrc = P;
         pre_sorted = true;
     }
