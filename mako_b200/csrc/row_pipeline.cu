@@ -366,6 +366,229 @@ __device__ void merge_pass(const unsigned long long* src, unsigned long long* ds
     }
 }
 
+// Where a row's results go (the output pointers of the launch), for the steps that live out of line.
+struct RowOut {
+    int32_t* token;
+    float* prob;
+    uint32_t* flags;
+    uint32_t* n_cand;
+    int32_t* accepted;
+    float* total_out;
+    int32_t* cand_ids;
+    float* cand_q;
+    uint32_t cand_cap;
+    int32_t id_offset;
+    unsigned long long* timing;
+    int mode;
+};
+
+// More candidates than the shared-memory sort holds, and no truncation orders them: the draw walks them in ascending
+// id (sampler.cpp:64-73). The exact weights are laid out by column in scratch (`qrow`) and one thread adds and walks
+// them in the reference's order and precision; the other threads stage tiles for it (`stage`: two tiles of shared
+// memory). Writes the row's results. Whole CTA.
+__device__ __noinline__ void wide_id_ordered(Smem& s, float* stage, const uint2* scratch, float* qrow, uint32_t n_raw,
+                                             uint32_t n, uint32_t V, float thr_final, float m, float inv_t, float minp_eff,
+                                             uint32_t row, uint32_t flags, float u_row, float u2_row, int32_t draft_row,
+                                             const RowOut o)
+{
+    const uint32_t tid = threadIdx.x;
+    for (uint32_t i = tid; i < V; i += kThreads)
+        qrow[i] = 0.0f;
+    __syncthreads();
+    for (uint32_t i = tid; i < n_raw; i += kThreads) {
+        const uint2 c = scratch[i];
+        if (!(__uint_as_float(c.x) >= thr_final))
+            continue;
+        const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), inv_t));
+        if (q >= minp_eff && q > 0.0f)
+            qrow[c.y] = q;
+    }
+    __threadfence_block();
+    __syncthreads();
+    const int32_t draft_col = (o.mode == kModeVerify) ? (draft_row - o.id_offset) : -1;
+    float total = 0.0f, q_draft = 0.0f;
+    // pass 0: float total (and the draft's weight); pass 1: the walk
+    float r = 0.0f, walk_total = 0.0f, eps = 0.0f;
+    int32_t tok = -1, last = -1, acc = 0;
+    float prob = 0.0f, last_q = 0.0f;
+    bool first = true, done = false, skip_draft = false;
+    uint32_t emitted = 0;
+    for (int pass = 0; pass < 2 && !done; ++pass) {
+        for (uint32_t t = 0; t * kTile < V && !done; ++t) {
+            const uint32_t base = t * kTile, n_t = min((uint32_t)kTile, V - base);
+            float* buf = stage + (t & 1) * kTile;
+            for (uint32_t e = tid; e < n_t; e += kThreads)
+                buf[e] = qrow[base + e];
+            __syncthreads();
+            if (tid == 0) {
+                if (pass == 0) {
+                    for (uint32_t e = 0; e < n_t; ++e) {
+                        const float q = buf[e];
+                        if (q > 0.0f) {
+                            total = __fadd_rn(total, q);
+                            if ((int32_t)(base + e) == draft_col)
+                                q_draft = q;
+                            if (emitted < o.cand_cap) {
+                                if (o.cand_ids) o.cand_ids[(size_t)row * o.cand_cap + emitted] = (int32_t)(base + e) + o.id_offset;
+                                if (o.cand_q) o.cand_q[(size_t)row * o.cand_cap + emitted] = q;
+                            }
+                            ++emitted;
+                        }
+                    }
+                } else {
+                    for (uint32_t e = 0; e < n_t && !done; ++e) {
+                        const float q = buf[e];
+                        if (!(q > 0.0f) || (skip_draft && (int32_t)(base + e) == draft_col))
+                            continue;
+                        last = (int32_t)(base + e);
+                        last_q = q;
+                        if (r < q) {
+                            tok = last;
+                            prob = __fdiv_rn(q, walk_total);
+                            if ((!first && r < eps) || __fsub_rn(q, r) < eps)
+                                s.flags = 1; // upper boundary: cleared below if this was the last candidate
+                            s.n_final = (!first && r < eps) ? 2u : 0u;
+                            done = true;
+                        } else {
+                            r = __fsub_rn(r, q);
+                            first = false;
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            if (pass == 1) {
+                // the walking thread publishes "done" through shared memory
+                if (tid == 0)
+                    s.nsurv = done ? 0xffffffffu : n;
+                __syncthreads();
+                done = s.nsurv == 0xffffffffu;
+            }
+        }
+        if (pass == 0) {
+            // decide what the walk does (sampler.cpp:100-106 for verify)
+            if (tid == 0) {
+                walk_total = total;
+                if (o.mode == kModeVerify) {
+                    acc = __fmul_rn(u_row, total) < q_draft;
+                    if (acc) {
+                        tok = draft_col + o.id_offset;
+                        prob = __fdiv_rn(q_draft, total);
+                    } else {
+                        skip_draft = true;
+                        walk_total = __fsub_rn(total, q_draft);
+                    }
+                }
+                const float uu = (o.mode == kModeVerify) ? u2_row : u_row;
+                r = __fmul_rn(uu, walk_total);
+                eps = 1e-6f * walk_total;
+                s.n_final = 0;
+                s.flags = 0;
+                s.nsurv = (o.mode == kModeDistOnly || acc) ? 0xffffffffu : n;
+            }
+            __syncthreads();
+            done = s.nsurv == 0xffffffffu;
+        }
+    }
+    if (tid == 0) {
+        if (o.mode == kModeDistOnly) {
+            tok = -1;
+        } else if (tok < 0) { // rounding: the last candidate
+            tok = last;
+            prob = __fdiv_rn(last_q, walk_total);
+        } else if (!acc && o.mode != kModeDistOnly) {
+            // near-boundary report: lower boundary always counts; the upper one only if a candidate follows
+            bool more = false;
+            for (uint32_t c = (uint32_t)tok + 1; c < V && !more; ++c)
+                if (qrow[c] > 0.0f && !(skip_draft && (int32_t)c == draft_col))
+                    more = true;
+            if (s.n_final == 2u || (s.flags && more))
+                flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
+        }
+        if (o.token) o.token[row] = (tok >= 0 && !(acc)) ? tok + o.id_offset : tok;
+        if (o.prob) o.prob[row] = prob;
+        if (o.flags) o.flags[row] = flags;
+        if (o.n_cand) o.n_cand[row] = n;
+        if (o.accepted) o.accepted[row] = acc;
+        if (o.total_out) o.total_out[row] = total;
+        if (o.timing) o.timing[(size_t)row * 64 + 3] = global_ns();
+    }
+}
+
+// sampler.cpp:44-61 for a list longer than one warp walks: the shortest prefix of the sorted list whose double sum
+// reaches top_p * total. The sums are taken by the whole CTA (each thread a contiguous run of the list, then a scan
+// over threads); their rounding differs from the reference's left-to-right sum by far less than the margin inside
+// which a decision is reported. Returns the prefix length; bit 31 set: the list ended before the nucleus did
+// (`need_sum` rows), or the decision lies within the margin. `total_need`/`band_need`: the row total and its margin
+// when the total covers more than the list (`use_row_total`).
+__device__ __noinline__ uint32_t wide_top_p(Smem& s, const unsigned long long* ksrc, uint32_t n, float top_p, bool need_sum,
+                                            bool use_row_total, double total_need, double band_need)
+{
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t per = (n + kThreads - 1) / kThreads;
+    const uint32_t r0 = min(tid * per, n), r1 = min(r0 + per, n);
+    double mine = 0.0;
+    for (uint32_t r = r0; r < r1; ++r)
+        mine += (double)__uint_as_float(~(uint32_t)(ksrc[r] >> 32));
+    double inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double y = __shfl_up_sync(0xffffffffu, inc, o);
+        if ((int)lane >= o)
+            inc += y;
+    }
+    __syncthreads(); // warp_sum may still be read
+    if (lane == 31)
+        s.warp_sum[warp] = inc;
+    if (tid == 0)
+        s.n_final = n;
+    __syncthreads();
+    double before = inc - mine, list_total = 0.0;
+    for (uint32_t w = 0; w < (uint32_t)(kThreads / 32); ++w) {
+        if (w < warp)
+            before += s.warp_sum[w];
+        list_total += s.warp_sum[w];
+    }
+    double total, band;
+    if (use_row_total) {
+        total = total_need;
+        band = band_need + 0x1p-36 * total;
+    } else {
+        total = list_total;
+        band = 0x1p-36 * total;
+    }
+    const double want = (double)top_p * total;
+    {
+        double run = before;
+        for (uint32_t r = r0; r < r1; ++r) {
+            run += (double)__uint_as_float(~(uint32_t)(ksrc[r] >> 32));
+            if (!(run < want)) {
+                atomicMin(&s.n_final, r + 1u);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const uint32_t k = s.n_final; // candidates taken: the first count whose sum is not below `want`, else all
+    __syncthreads();
+    {
+        double run = before;
+        for (uint32_t r = r0; r < r1; ++r) {
+            const double prev = run;
+            run += (double)__uint_as_float(~(uint32_t)(ksrc[r] >> 32));
+            if (r + 1u == k) {
+                s.warp_sum[0] = run;
+                s.warp_sum[1] = prev;
+            }
+        }
+    }
+    __syncthreads();
+    const double run = s.warp_sum[0], prev = s.warp_sum[1];
+    const bool unsure = (need_sum && run < want) ||
+                        (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)));
+    return k | (unsure ? 0x80000000u : 0u);
+}
+
 // top_p alone, a long collected list: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was
 // not collected belongs to that tail; collected elements can join it from the bottom for as long as the tail stays
 // within the budget. Approximate weights decide the cut (with margins) and raise s.thr_topk_key; the nucleus itself
@@ -1191,132 +1414,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         a.timing[(size_t)row * 64 + 11] = global_ns();
     }
     if (!overflow && n > (uint32_t)kSortCap && !cfg.use_topp && !(cfg.top_k > 0 && cfg.top_k < n)) {
-        // More candidates than the shared-memory sort holds, and no truncation orders them: the draw walks them
-        // in ascending id (sampler.cpp:64-73). The exact weights are laid out by column in scratch and one thread
-        // adds and walks them in the reference's order and precision; the other threads stage tiles for it.
-        const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
-        for (uint32_t i = tid; i < V; i += kThreads)
-            qrow[i] = 0.0f;
-        __syncthreads();
-        for (uint32_t i = tid; i < n_raw; i += kThreads) {
-            const uint2 c = scratch[i];
-            if (!(__uint_as_float(c.x) >= thr_final))
-                continue;
-            const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
-            if (q >= cfg.minp_eff && q > 0.0f)
-                qrow[c.y] = q;
-        }
-        __threadfence_block();
-        __syncthreads();
-        float* stage = reinterpret_cast<float*>(dyn + kOffKeys);
-        const int32_t draft_col = (a.mode == kModeVerify) ? (draft_row - a.id_offset) : -1;
-        float total = 0.0f, q_draft = 0.0f;
-        // pass 0: float total (and the draft's weight); pass 1: the walk
-        float r = 0.0f, walk_total = 0.0f, eps = 0.0f;
-        int32_t tok = -1, last = -1, acc = 0;
-        float prob = 0.0f, last_q = 0.0f;
-        bool first = true, done = false, skip_draft = false;
-        uint32_t emitted = 0;
-        for (int pass = 0; pass < 2 && !done; ++pass) {
-            for (uint32_t t = 0; t * kTile < V && !done; ++t) {
-                const uint32_t base = t * kTile, n_t = min((uint32_t)kTile, V - base);
-                float* buf = stage + (t & 1) * kTile;
-                for (uint32_t e = tid; e < n_t; e += kThreads)
-                    buf[e] = qrow[base + e];
-                __syncthreads();
-                if (tid == 0) {
-                    if (pass == 0) {
-                        for (uint32_t e = 0; e < n_t; ++e) {
-                            const float q = buf[e];
-                            if (q > 0.0f) {
-                                total = __fadd_rn(total, q);
-                                if ((int32_t)(base + e) == draft_col)
-                                    q_draft = q;
-                                if (emitted < a.cand_cap) {
-                                    if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + emitted] = (int32_t)(base + e) + a.id_offset;
-                                    if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + emitted] = q;
-                                }
-                                ++emitted;
-                            }
-                        }
-                    } else {
-                        for (uint32_t e = 0; e < n_t && !done; ++e) {
-                            const float q = buf[e];
-                            if (!(q > 0.0f) || (skip_draft && (int32_t)(base + e) == draft_col))
-                                continue;
-                            last = (int32_t)(base + e);
-                            last_q = q;
-                            if (r < q) {
-                                tok = last;
-                                prob = __fdiv_rn(q, walk_total);
-                                if ((!first && r < eps) || __fsub_rn(q, r) < eps)
-                                    s.flags = 1; // upper boundary: cleared below if this was the last candidate
-                                s.n_final = (!first && r < eps) ? 2u : 0u;
-                                done = true;
-                            } else {
-                                r = __fsub_rn(r, q);
-                                first = false;
-                            }
-                        }
-                    }
-                }
-                __syncthreads();
-                if (pass == 1) {
-                    // the walking thread publishes "done" through shared memory
-                    if (tid == 0)
-                        s.nsurv = done ? 0xffffffffu : n;
-                    __syncthreads();
-                    done = s.nsurv == 0xffffffffu;
-                }
-            }
-            if (pass == 0) {
-                // decide what the walk does (sampler.cpp:100-106 for verify)
-                if (tid == 0) {
-                    walk_total = total;
-                    if (a.mode == kModeVerify) {
-                        acc = __fmul_rn(u_row, total) < q_draft;
-                        if (acc) {
-                            tok = draft_col + a.id_offset;
-                            prob = __fdiv_rn(q_draft, total);
-                        } else {
-                            skip_draft = true;
-                            walk_total = __fsub_rn(total, q_draft);
-                        }
-                    }
-                    const float uu = (a.mode == kModeVerify) ? u2_row : u_row;
-                    r = __fmul_rn(uu, walk_total);
-                    eps = 1e-6f * walk_total;
-                    s.n_final = 0;
-                    s.flags = 0;
-                    s.nsurv = (a.mode == kModeDistOnly || acc) ? 0xffffffffu : n;
-                }
-                __syncthreads();
-                done = s.nsurv == 0xffffffffu;
-            }
-        }
-        if (tid == 0) {
-            if (a.mode == kModeDistOnly) {
-                tok = -1;
-            } else if (tok < 0) { // rounding: the last candidate
-                tok = last;
-                prob = __fdiv_rn(last_q, walk_total);
-            } else if (!acc && a.mode != kModeDistOnly) {
-                // near-boundary report: lower boundary always counts; the upper one only if a candidate follows
-                bool more = false;
-                for (uint32_t c = (uint32_t)tok + 1; c < V && !more; ++c)
-                    if (qrow[c] > 0.0f && !(skip_draft && (int32_t)c == draft_col))
-                        more = true;
-                if (s.n_final == 2u || (s.flags && more))
-                    flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
-            }
-            if (a.token) a.token[row] = (tok >= 0 && !(acc)) ? tok + a.id_offset : tok;
-            if (a.prob) a.prob[row] = prob;
-            if (a.flags) a.flags[row] = flags;
-            if (a.n_cand) a.n_cand[row] = n;
-            if (a.accepted) a.accepted[row] = acc;
-            if (a.total_out) a.total_out[row] = total;
-            if (a.timing) a.timing[(size_t)row * 64 + 3] = global_ns();
-        }
+        const RowOut o = {a.token, a.prob, a.flags, a.n_cand, a.accepted, a.total_out, a.cand_ids, a.cand_q,
+                          a.cand_cap, a.id_offset, a.timing, a.mode};
+        wide_id_ordered(s, reinterpret_cast<float*>(dyn + kOffKeys), scratch, qrow, n_raw, n, V,
+                        fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key)), m, cfg.inv_t, cfg.minp_eff, row,
+                        flags, u_row, u2_row, draft_row, o);
         return;
     }
     const unsigned long long* ksrc = keys; // the ordered list: shared memory, or the row's scratch for a long one
@@ -1435,78 +1537,15 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const bool short_list = n <= 128u; // one warp does it all, in the reference's own order, without CTA barriers
     bool retry = false; // first launch, top_p alone: what was kept does not settle the nucleus; the second pass will
     if (cfg.use_topp && !short_list) {
-        // sampler.cpp:44-61: the shortest prefix of the sorted list whose double sum reaches top_p * total. The sums
-        // are taken by the whole CTA (each thread a contiguous run of the list, then a scan over threads); their
-        // rounding differs from the reference's left-to-right sum by far less than the margin inside which a
-        // decision is reported.
-        const uint32_t per = (n + kThreads - 1) / kThreads;
-        const uint32_t r0 = min(tid * per, n), r1 = min(r0 + per, n);
-        double mine = 0.0;
-        for (uint32_t r = r0; r < r1; ++r)
-            mine += (double)q_of(r);
-        double inc = mine;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const double y = __shfl_up_sync(0xffffffffu, inc, o);
-            if ((int)lane >= o)
-                inc += y;
-        }
-        __syncthreads(); // warp_sum may still be read
-        if (lane == 31)
-            s.warp_sum[warp] = inc;
-        if (tid == 0)
-            s.n_final = n;
-        __syncthreads();
-        double before = inc - mine, list_total = 0.0;
-        for (uint32_t w = 0; w < (uint32_t)(kThreads / 32); ++w) {
-            if (w < warp)
-                before += s.warp_sum[w];
-            list_total += s.warp_sum[w];
-        }
-        double total, band;
-        if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
-            total = total_need;
-            band = band_need + 0x1p-36 * total;
-        } else {
-            total = list_total;
-            band = 0x1p-36 * total;
-        }
-        const double want = (double)cfg.top_p * total;
-        {
-            double run = before;
-            for (uint32_t r = r0; r < r1; ++r) {
-                run += (double)q_of(r);
-                if (!(run < want)) {
-                    atomicMin(&s.n_final, r + 1u);
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-        const uint32_t k = s.n_final; // candidates taken: the first count whose sum is not below `want`, else all
-        __syncthreads();
-        {
-            double run = before;
-            for (uint32_t r = r0; r < r1; ++r) {
-                const double prev = run;
-                run += (double)q_of(r);
-                if (r + 1u == k) {
-                    s.warp_sum[0] = run;
-                    s.warp_sum[1] = prev;
-                }
-            }
-        }
-        __syncthreads();
-        const double run = s.warp_sum[0], prev = s.warp_sum[1];
-        // the collected list ended before the nucleus did, or the decision lies within the margin
-        if ((cfg.need_sum && run < want) ||
-            (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))) {
+        const uint32_t kk = wide_top_p(s, ksrc, n, cfg.top_p, cfg.need_sum, cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE),
+                                       total_need, band_need);
+        if (kk & 0x80000000u) {
             if (cfg.optimistic)
                 retry = true;
             else
                 flags |= MK_FLAG_GUARD_BAND;
         }
-        n = max(k, 1u);
+        n = max(kk & 0x7fffffffu, 1u);
     }
 
     if (a.timing && tid == 0)
