@@ -53,6 +53,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 
 // Bounded wait: gives up after `limit` probes and reports false, so that a lost copy or a logic error ends the
 // kernel with a status instead of hanging the GPU. (2^17 probes of up to 20 us each: a few seconds at most.)
+// The same wait by polling (no suspension): for the one lane whose reaction time is on a ring stage's round trip.
+// Bounded like the other: about a million probes.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22))
+{
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok)
+            return true;
+    }
+    return false;
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 17))
 {
     for (uint32_t i = 0; i < limit; ++i)

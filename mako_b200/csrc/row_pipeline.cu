@@ -949,8 +949,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             const float* src = lrow + (size_t)t * kTile;
             if (k > 0) {
                 bool ok = true;
-                if (lane == 0)
-                    ok = mbar_wait(&s.empty[st], (k - 1) & 1);
+                if (lane == 0) // polling: this lane's reaction time is on every stage's round trip
+                    ok = mbar_wait_poll(&s.empty[st], (k - 1) & 1);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     if (lane == 0)
