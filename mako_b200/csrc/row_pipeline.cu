@@ -759,12 +759,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // The history is read into registers first thing, all loads in flight together, so that their latency
     // overlaps the barrier set-up instead of being paid once per loop trip.
     constexpr int kHistPerThread = (kHistCap + kThreads - 1) / kThreads;
-    int32_t hv[kHistPerThread];
+    uint32_t hc[kHistPerThread]; // the entries as columns of this row (ids outside it: 0xffffffff, as past-the-end)
     if (has_hist && !long_history) { // = use_table
 #pragma unroll
         for (int i = 0; i < kHistPerThread; ++i) {
             const uint32_t j = (uint32_t)i * kThreads + tid;
-            hv[i] = (j < hlen) ? __ldg(hrow + j) : 0;
+            hc[i] = (j < hlen) ? (uint32_t)__ldg(hrow + j) - (uint32_t)a.id_offset : 0xffffffffu;
         }
     }
     // ---- shared-memory layout of the streaming phase ---------------------------------------------------------------
@@ -848,10 +848,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // counts by rank.
 #pragma unroll
         for (int hi = 0; hi < kHistPerThread; ++hi) {
-            const uint32_t j = (uint32_t)hi * kThreads + tid;
-            const int64_t col64 = (j < hlen) ? ((int64_t)hv[hi] - a.id_offset) : -1;
-            if (col64 >= 0 && col64 < (int64_t)V) {
-                const uint32_t col = (uint32_t)col64, bit = 1u << (col & 31u);
+            if (hc[hi] < V) { // unsigned: an id below the row's first column wraps past V
+                const uint32_t col = hc[hi], bit = 1u << (col & 31u);
                 if (!(*(volatile uint32_t*)&bitmap[col >> 5] & bit)) // skip the atomic once the bit is visible
                     if (!(atomicOr(&bitmap[col >> 5], bit) & bit))
                         own |= 1u << hi; // exactly one entry per distinct column sees its bit go from 0 to 1
@@ -866,10 +864,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             a.timing[(size_t)row * 64 + 8] = global_ns();
 #pragma unroll
         for (int hi = 0; hi < kHistPerThread; ++hi) {
-            const uint32_t j = (uint32_t)hi * kThreads + tid;
-            const int64_t col64 = (j < hlen) ? ((int64_t)hv[hi] - a.id_offset) : -1;
-            if (col64 >= 0 && col64 < (int64_t)V) {
-                const uint32_t col = (uint32_t)col64;
+            if (hc[hi] < V) {
+                const uint32_t col = hc[hi];
                 const uint32_t rank = wpre[col >> 5] + __popc(bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
                 atomicAdd(&counts[rank >> 1], 1u << ((rank & 1u) * 16u));
             }
@@ -910,7 +906,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             float pv[kHistPerThread];
 #pragma unroll
             for (int hi = 0; hi < kHistPerThread; ++hi) {
-                const uint32_t col = (uint32_t)(hv[hi] - a.id_offset);
+                const uint32_t col = hc[hi];
                 pc[hi] = (((own >> hi) & 1u) && col < span) ? col : 0xffffffffu;
                 const uint32_t c = (pc[hi] != 0xffffffffu) ? col : 0u;
                 pn[hi] = wpre[c >> 5] + __popc(bitmap[c >> 5] & ((1u << (c & 31u)) - 1u)); // rank
