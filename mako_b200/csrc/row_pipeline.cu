@@ -215,6 +215,23 @@ __device__ __forceinline__ unsigned long long pack_by_column(float q, uint32_t c
     return ((unsigned long long)col << 32) | __float_as_uint(q);
 }
 
+// Position of the n-th set bit (n = 0: the lowest) of a word that has more than n bits set: five halvings by
+// popcount (the library's find-n-th-set is a loop over the bits).
+__device__ __forceinline__ uint32_t nth_set_bit(uint32_t w, uint32_t n)
+{
+    uint32_t pos = 0;
+#pragma unroll
+    for (uint32_t width = 16; width > 0; width >>= 1) {
+        const uint32_t c = (uint32_t)__popc(w & ((1u << width) - 1u));
+        if (n >= c) {
+            n -= c;
+            pos += width;
+            w >>= width;
+        }
+    }
+    return pos;
+}
+
 // Penalties (sampler.cpp:23-28) for the generated columns with ranks [r_lo, r_hi) — the ones whose bitmap words lie
 // in [w_lo, w_hi) — spread evenly over n_thr threads (this one is `thr`): a rank is turned back into its column by a
 // binary search over the per-word ranks and a find-n-th-set-bit in the word, and indexes the count directly. Every
@@ -232,7 +249,7 @@ __device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t*
             else
                 hi = mid;
         }
-        const uint32_t bit = __fns(bitmap[lo], 0u, (int)(r - (uint32_t)wpre[lo]) + 1);
+        const uint32_t bit = nth_set_bit(bitmap[lo], r - (uint32_t)wpre[lo]);
         const uint32_t n = (counts[r >> 1] >> ((r & 1u) * 16u)) & 0xffffu;
         const uint32_t loc = (lo << 5) + bit - col0;
         tile[loc] = penalise(tile[loc], n, cfg);
