@@ -3,26 +3,31 @@
 // What it replaces: mako::gen::Sampler::distribution / draw / sample / verify (src/gen/sampler.cpp:20-107), which
 // the reference runs on the host, one row at a time, over a copy of the logits.
 //
-// Shape of the kernel (352 threads = 11 warps, ~110 KB shared memory, two CTAs per SM):
-//   warp 0        producer: streams the row through a 4-stage ring of 16 KB tiles with untiled bulk asynchronous
-//                 copies (TMA, cp.async.bulk, no multicast), completion on an mbarrier per stage; the first tiles are
-//                 requested before the set-up so that they fly meanwhile.
+// Shape of the kernel (352 threads = 11 warps, 113 KB shared memory laid out per row, two CTAs per SM):
+//   warp 0        producer: streams the row through a ring of 16 KB tiles — five stages beside a history's tables,
+//                 seven without — with untiled bulk asynchronous copies (TMA, cp.async.bulk, no multicast, L2
+//                 evict-first), completion on an mbarrier per stage; the first stages are requested before the
+//                 set-up so that they fly meanwhile.
 //   set-up        all warps: the token history becomes a bitmap of generated columns, the rank of each bitmap
 //                 word's first set bit (prefix popcount) and, by rank, the count of each generated column — the
-//                 multiset the reference keeps in an unordered_map (sampler.cpp:15-18). The penalties of the tiles
-//                 that have landed by then (the dense head of the history) are applied by all warps, spread evenly
-//                 by rank (binary search over the word ranks + find-n-th-set-bit).
+//                 multiset the reference keeps in an unordered_map (sampler.cpp:15-18). The history entry that set
+//                 a column's bit owns the column; owners apply the penalties to the tiles that have landed by then
+//                 (the dense head of the history).
 //   warps 1-2     fix-up: each owns every other tile; once it has landed, apply the sparse edits in shared memory —
 //                 logit bias, then the repetition / presence / frequency penalties of the tile's generated columns,
-//                 each once with its count (sampler.cpp:23-28) — and release it to the readers.
+//                 each once with its count (sampler.cpp:23-28), found by rank (binary search over the word ranks,
+//                 then the n-th set bit of the word) — and release it to the readers.
 //   warps 3-10    readers: 128-bit shared loads, allowed-token mask, running row maximum (warp shuffles), and
 //                 collection of every element that can still become a candidate: the keep thresholds of min_p,
 //                 top_k and top_p are all lower-bounded by a function of the running maximum (or of a histogram of
 //                 order-preserving float keys for top_k) that only rises while the row streams, so filtering with
-//                 the current bound keeps a superset of the final candidates.
+//                 the current bound keeps a superset of the final candidates. The loop exists in four variants.
 //   all warps     finish: exact weights q = expf((l - max) * inv_t) for the few collected elements with the host
 //                 library's float exponential (device_expf.cuh), min_p, top_k, top_p, and the sequential float
-//                 walk of the draw — in the reference's precision and order, because token ids depend on both.
+//                 total and walk of the draw — in the reference's precision and order, because token ids depend on
+//                 both. Steps only unusual rows need (long lists) live in functions of their own.
+//   second pass   top_p alone: the first launch keeps the 256 largest elements; a row whose nucleus that does not
+//                 settle marks itself, and a second launch of this kernel streams the marked rows again.
 //
 // Numeric contract (what makes ids bit-exact): IEEE division and no FMA contraction in the penalties and in
 // (l - max) * inv_t; q through expf_host_exact; top_p sums in double; total and the walk in float, left to right.
