@@ -833,11 +833,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (cfg.hist_mode)
         for (uint32_t i = tid; i < kBins; i += kThreads)
             hist[i] = 0;
-    if (use_table) {
-        for (uint32_t i = tid; i < bm_words; i += kThreads)
-            bitmap[i] = 0;
-        for (uint32_t i = tid; i < kHistCap / 2; i += kThreads)
-            counts[i] = 0;
+    if (use_table) { // bitmap, ranks and counts are contiguous and 16-byte aligned: cleared with 128-bit stores
+        uint4* const z = reinterpret_cast<uint4*>(bitmap);
+        const uint32_t nz = (uint32_t)(reinterpret_cast<unsigned char*>(counts + kHistCap / 2) -
+                                       reinterpret_cast<unsigned char*>(bitmap)) / 16u;
+        for (uint32_t i = tid; i < nz; i += kThreads)
+            z[i] = make_uint4(0u, 0u, 0u, 0u);
     }
     uint32_t tiles_issued = 0;
     __syncthreads();
