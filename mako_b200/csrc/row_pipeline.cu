@@ -752,13 +752,26 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const uint32_t n_tiles = (V + kTile - 1) / kTile;
     const float* __restrict__ lrow = a.logits + (size_t)row * a.ld;
     const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
-    const RowCfg cfg = make_cfg(prm, V, a.mode, a.vp_k, a.pass);
-
+    // Whether the history matters is known from three comparisons; its loads (the first thing the set-up waits for)
+    // are issued before the rest of the parameters is worked out.
     const uint32_t hlen_all = a.history ? (a.history_len ? (uint32_t)max(a.history_len[row], 0) : a.n_history) : 0u;
-    const bool has_hist = !cfg.greedy && cfg.pen_active && hlen_all > 0;
+    const bool has_hist = !(prm.temperature <= 0.0f) && hlen_all > 0 &&
+                          !(prm.repetition_penalty == 1.0f && prm.presence_penalty == 0.0f && prm.frequency_penalty == 0.0f);
     const uint32_t hlen = has_hist ? hlen_all : 0u;
     const int32_t* __restrict__ hrow = a.history ? a.history + (size_t)row * a.history_ld : nullptr;
     const bool long_history = hlen > (uint32_t)kHistCap || V > kMaxBitmapVocab;
+    // The history is read into registers first thing, all loads in flight together, so that their latency
+    // overlaps the barrier set-up instead of being paid once per loop trip.
+    constexpr int kHistPerThread = (kHistCap + kThreads - 1) / kThreads;
+    uint32_t hc[kHistPerThread]; // the entries as columns of this row (ids outside it: 0xffffffff, as past-the-end)
+    if (has_hist && !long_history) { // = use_table
+#pragma unroll
+        for (int i = 0; i < kHistPerThread; ++i) {
+            const uint32_t j = (uint32_t)i * kThreads + tid;
+            hc[i] = (j < hlen) ? (uint32_t)__ldg(hrow + j) - (uint32_t)a.id_offset : 0xffffffffu;
+        }
+    }
+    const RowCfg cfg = make_cfg(prm, V, a.mode, a.vp_k, a.pass);
     const uint32_t nb = a.bias ? a.n_bias : 0u;
     const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
     const bool has_fix = nb > 0 || has_hist; // work for the fix-up warps
@@ -778,17 +791,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
     const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
     const int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
-    // The history is read into registers first thing, all loads in flight together, so that their latency
-    // overlaps the barrier set-up instead of being paid once per loop trip.
-    constexpr int kHistPerThread = (kHistCap + kThreads - 1) / kThreads;
-    uint32_t hc[kHistPerThread]; // the entries as columns of this row (ids outside it: 0xffffffff, as past-the-end)
-    if (has_hist && !long_history) { // = use_table
-#pragma unroll
-        for (int i = 0; i < kHistPerThread; ++i) {
-            const uint32_t j = (uint32_t)i * kThreads + tid;
-            hc[i] = (j < hlen) ? (uint32_t)__ldg(hrow + j) - (uint32_t)a.id_offset : 0xffffffffu;
-        }
-    }
     // ---- shared-memory layout of the streaming phase ---------------------------------------------------------------
     const bool use_table = has_hist && !long_history;
     const uint32_t bm_words = (V + 31u) / 32u;
