@@ -39,6 +39,7 @@ typedef enum mk_status {
 #define MK_FLAG_OVERFLOW          0x010u /* more candidates than the handle's capacity: token = -1 */
 #define MK_FLAG_VP_TRUNCATED      0x020u /* vocab-parallel: the nucleus may reach past a shard's top-k list */
 #define MK_FLAG_TIMEOUT           0x040u /* a bounded device-side wait ran out: token = -1 */
+#define MK_FLAG_HISTORY_FULL      0x100u /* mk_decode_commit: the row's history buffer is full, the token was not appended */
 
 /* Field for field mako::gen::SamplingParams (src/gen/sampler.hpp:12-20). temperature <= 0 selects greedy. */
 typedef struct mk_sampling_params {
@@ -146,6 +147,19 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
  * if every draft was kept. */
 int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                     int32_t* n_kept, int32_t* next_token, void* stream);
+
+/* The bookkeeping of the reference's decode loop (src/gen/session.cpp:416-444) on the device, so that a step needs
+ * no host round trip between the sampler and the next forward pass. Per row b: token = forced[b] if `forced` is given
+ * and forced[b] >= 0 (the reference bypasses the sampler for a forced token — tool_choice, the reasoning budget,
+ * src/gen/session.hpp:43-45 — without drawing, but still accept()s it), else sampled[b]. The token is written to
+ * committed[b] and next_input[b] (both optional: the next step's input id) and appended to the row's history,
+ * history[b][history_len[b]++] — what Sampler::accept does (sampler.cpp:15-18); the next sample call reads the same
+ * buffers through mk_rows.history / history_len. A row whose history is full keeps its length and gets
+ * MK_FLAG_HISTORY_FULL or-ed into flags[b] (optional); a sampled token < 0 (a failed row) is not committed.
+ * All pointers are device pointers. */
+int mk_decode_commit(mk_sampler* s, uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
+                     uint64_t history_ld, uint32_t history_cap, int32_t* history_len, int32_t* next_input,
+                     int32_t* committed, uint32_t* flags, void* stream);
 
 /* Vocab-parallel sampling, step 1 of 2 (no counterpart in the reference, which runs on one device): each shard
  * writes one record per row — its maximum, its sum of exp((l - max)/T) and its `k` best candidates (<= 64) — of

@@ -6,7 +6,7 @@ CPU.
 """
 _SAMPLER = {"BatchSampler", "SampleResult", "Sampler", "SamplingParams", "check_sampling", "pack_bias", "pack_params"}
 _LIB = {"MakoError", "lib", "FLAG_ALL_MASKED", "FLAG_GUARD_BAND", "FLAG_NEAR_CDF_BOUNDARY", "FLAG_NO_CANDIDATE",
-        "FLAG_OVERFLOW", "FLAG_TIMEOUT", "FLAG_VP_TRUNCATED"}
+        "FLAG_OVERFLOW", "FLAG_TIMEOUT", "FLAG_HISTORY_FULL", "FLAG_VP_TRUNCATED"}
 __all__ = sorted(_SAMPLER | _LIB | {"version", "synth"})
 
 

@@ -24,6 +24,7 @@ FLAG_ALL_MASKED = 0x008
 FLAG_OVERFLOW = 0x010
 FLAG_VP_TRUNCATED = 0x020
 FLAG_TIMEOUT = 0x040
+FLAG_HISTORY_FULL = 0x100
 
 
 class SamplingParamsC(C.Structure):
@@ -101,6 +102,7 @@ def _load() -> C.CDLL:
     lib.mk_sampler_verify_batch.argtypes = [vp, C.POINTER(RowsC), vp, vp, vp, C.POINTER(SampleOutC), vp, vp]
     lib.mk_sampler_verify_pq_batch.argtypes = [vp, C.POINTER(RowsC), vp, C.c_uint64, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.mk_spec_resolve.argtypes = [vp, C.c_uint32, C.c_uint32, vp, vp, vp, vp, vp]
+    lib.mk_decode_commit.argtypes = [vp, C.c_uint32, vp, vp, vp, C.c_uint64, C.c_uint32, vp, vp, vp, vp, vp]
     lib.mk_vp_record_bytes.restype = C.c_uint32
     lib.mk_vp_record_bytes.argtypes = [C.c_uint32]
     lib.mk_sampler_vp_local.argtypes = [vp, C.POINTER(RowsC), C.c_uint32, vp, vp]

@@ -440,4 +440,41 @@ cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* a
     return cudaGetLastError();
 }
 
+// ---- bookkeeping of one decode step (src/gen/session.cpp:416-444) ----------------------------------------------------
+__global__ void decode_commit_kernel(uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
+                                     uint64_t history_ld, uint32_t history_cap, int32_t* history_len,
+                                     int32_t* next_input, int32_t* committed, uint32_t* flags)
+{
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch)
+        return;
+    // a forced token bypasses the sampler but is accepted like any other (session.cpp:441-444)
+    const int32_t t = (forced && forced[b] >= 0) ? forced[b] : sampled[b];
+    if (committed)
+        committed[b] = t;
+    if (t < 0) // the row failed (overflow, timeout): nothing to commit
+        return;
+    if (next_input)
+        next_input[b] = t;
+    const int32_t len = history_len[b];
+    if (len >= 0 && (uint32_t)len < history_cap) {
+        history[(size_t)b * history_ld + (uint32_t)len] = t; // Sampler::accept (sampler.cpp:15-18)
+        history_len[b] = len + 1;
+    } else if (flags) {
+        flags[b] |= MK_FLAG_HISTORY_FULL;
+    }
+}
+
+cudaError_t launch_decode_commit(uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
+                                 uint64_t history_ld, uint32_t history_cap, int32_t* history_len, int32_t* next_input,
+                                 int32_t* committed, uint32_t* flags, cudaStream_t stream)
+{
+    if (batch == 0)
+        return cudaSuccess;
+    decode_commit_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(batch, sampled, forced, history, history_ld,
+                                                                   history_cap, history_len, next_input, committed,
+                                                                   flags);
+    return cudaGetLastError();
+}
+
 } // namespace mk

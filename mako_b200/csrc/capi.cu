@@ -404,6 +404,21 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
     return MK_OK;
 }
 
+int mk_decode_commit(mk_sampler* s, uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
+                     uint64_t history_ld, uint32_t history_cap, int32_t* history_len, int32_t* next_input,
+                     int32_t* committed, uint32_t* flags, void* stream)
+{
+    if (!s || !sampled || !history || !history_len)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_decode_commit: sampled, history and history_len are required");
+    if (history_ld < history_cap)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_decode_commit: history_ld %llu below history_cap %u",
+                    (unsigned long long)history_ld, history_cap);
+    DeviceGuard g(s->device);
+    MK_CUDA(mk::launch_decode_commit(batch, sampled, forced, history, history_ld, history_cap, history_len, next_input,
+                                     committed, flags, (cudaStream_t)stream));
+    return MK_OK;
+}
+
 int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                     int32_t* n_kept, int32_t* next_token, void* stream)
 {

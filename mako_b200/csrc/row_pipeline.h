@@ -94,6 +94,10 @@ cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream);
 cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                                 int32_t* n_kept, int32_t* next_token, cudaStream_t stream);
 
+cudaError_t launch_decode_commit(uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
+                                 uint64_t history_ld, uint32_t history_cap, int32_t* history_len, int32_t* next_input,
+                                 int32_t* committed, uint32_t* flags, cudaStream_t stream);
+
 // Test hook: y[i] = expf_host_exact(x[i]).
 cudaError_t launch_expf_probe(const float* x, float* y, uint64_t n, cudaStream_t stream);
 

@@ -220,6 +220,19 @@ class BatchSampler:
         return SampleResult(self.token[:b], self.prob[:b], self.flags[:b], self.n_cand[:b],
                             accepted=self.accepted[:b], draft_token=self.draft_token[:b])
 
+    def decode_commit(self, sampled: torch.Tensor, history: torch.Tensor, history_len: torch.Tensor, *, forced=None,
+                      next_input=None, flags=None) -> torch.Tensor:
+        """One decode step's bookkeeping on the device (src/gen/session.cpp:416-444): forced tokens replace sampled
+        ones, the token is appended to each row's history (history [B, cap] int32, history_len [B] int32, both
+        updated in place) and written to next_input. Returns the committed tokens [B]."""
+        b = sampled.shape[0]
+        assert history.dtype == torch.int32 and history_len.dtype == torch.int32 and history.stride(1) == 1
+        committed = torch.empty(b, dtype=torch.int32, device=self.device)
+        check(lib.mk_decode_commit(self._h, b, sampled.data_ptr(), _ptr(forced), history.data_ptr(), history.stride(0),
+                                   history.shape[1], history_len.data_ptr(), _ptr(next_input), committed.data_ptr(),
+                                   _ptr(flags), _stream_ptr(self.device)))
+        return committed
+
     def spec_resolve(self, accepted: torch.Tensor, token: torch.Tensor):
         """accepted/token: [n_seq, n_pos] int32. Returns (n_kept [n_seq], next_token [n_seq])."""
         n_seq, n_pos = accepted.shape
