@@ -7,7 +7,7 @@ Configurations (synthetic, seeded; see mako_b200/csrc/synth.cpp):
   1  256 x 129280, 4096-id histories, penalties, T 0.8 / top_p 0.9 / min_p 0.05
   2  128 x 151552, 2 % allowed-token mask + 64 bias pairs, T 1 / top_p 1 draw, and the greedy variant
   3  320 positions x 129280, target + drafter logits, p/q rejection sampling, T 0.6 / top_p 0.95
-  4  1024 x 151552 as config 1 without min_p: single launch (row-sharded, N=1) and the vocab-parallel path with
+  4  1024 x 151552 as config 1 without min_p: one sample call (row-sharded, N=1) and the vocab-parallel path with
      8 column shards emulated on one GPU (8 local launches + merge; no all-gather on one GPU)
 Time is CUDA-event time of the launches alone with inputs resident in HBM, at least four distinct input sets
 (larger than L2 in total) cycled; bytes are the algorithmic bytes of the configuration.
@@ -119,7 +119,7 @@ def main():
     s = BatchSampler(v, b)
     p = SamplingParams(temperature=0.8, top_p=0.9, repetition_penalty=1.1, presence_penalty=0.5, frequency_penalty=0.3)
     us = _time(lambda k: s.sample(sets[k % 2]["logits"], p, sets[k % 2]["u"], **sets[k % 2]["kw"]), max(args.steps // 4, 20))
-    report("4 1024 x 151552 one launch (row-sharded, N=1)", us, b, b * lib.mk_row_bytes(v, h, 0, 0, 1))
+    report("4 1024 x 151552 row-sharded, N=1 (first launch + second pass)", us, b, b * lib.mk_row_bytes(v, h, 0, 0, 1))
     fl = s.flags[:b].cpu().numpy()
     nc = s.n_cand[:b].cpu().numpy()
     print(json.dumps(dict(config="4 row flags", overflow=int(((fl & 0x10) != 0).sum()),
