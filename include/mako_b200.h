@@ -148,6 +148,16 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
 int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                     int32_t* n_kept, int32_t* next_token, void* stream);
 
+/* The logit test of the reference's reasoning budget (ReasoningBudget::forced, src/server/openai.cpp:596-603): in
+ * the budget's last stretch the closing token is forced as soon as it is among the k = 3 largest raw logits. Per row
+ * b: above[b] = number of logits[b][i] strictly greater than logits[b][token[b]] (NaN never counts), forced[b] =
+ * token[b] if above[b] < k, else -1; a token[b] outside [0, n_vocab) forces nothing (forced -1, above 0xffffffff).
+ * `forced` feeds mk_decode_commit directly; either output may be NULL. The budget's counters (which rows are in the
+ * last stretch) stay with the caller: rows not in it pass token -1. All pointers are device pointers; one streaming
+ * pass over the rows (4 bytes per column). */
+int mk_rank_force(mk_sampler* s, const float* logits, uint64_t ld, uint32_t batch, uint32_t n_vocab,
+                  const int32_t* token, uint32_t k, int32_t* forced, uint32_t* above, void* stream);
+
 /* The bookkeeping of the reference's decode loop (src/gen/session.cpp:416-444) on the device, so that a step needs
  * no host round trip between the sampler and the next forward pass. Per row b: token = forced[b] if `forced` is given
  * and forced[b] >= 0 (the reference bypasses the sampler for a forced token — tool_choice, the reasoning budget,

@@ -440,6 +440,71 @@ cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* a
     return cudaGetLastError();
 }
 
+// ---- "is this token among the k largest raw logits" (ReasoningBudget::forced, src/server/openai.cpp:596-603) --------
+// One CTA per row streams the row once with 128-bit loads and counts the logits strictly greater than the token's
+// (NaN compares false, as in the reference's loop). HBM-bound: 4 bytes per column.
+constexpr int kRankThreads = 512;
+__global__ void __launch_bounds__(kRankThreads) rank_force_kernel(const float* logits, uint64_t ld, uint32_t n_vocab,
+                                                                 const int32_t* token, uint32_t k, int32_t* forced,
+                                                                 uint32_t* above)
+{
+    __shared__ uint32_t s_part[kRankThreads / 32];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const int32_t t = token[row];
+    if (t < 0 || (uint32_t)t >= n_vocab) { // no such token in this vocabulary: nothing is forced (openai.cpp:595)
+        if (tid == 0) {
+            if (forced) forced[row] = -1;
+            if (above) above[row] = 0xffffffffu;
+        }
+        return;
+    }
+    const float* lrow = logits + (size_t)row * ld;
+    const float v = __ldg(lrow + t);
+    uint32_t cnt = 0;
+    if (((reinterpret_cast<uintptr_t>(lrow) & 15u) == 0)) {
+        const float4* p4 = reinterpret_cast<const float4*>(lrow);
+        const uint32_t n4 = n_vocab / 4u;
+        uint32_t i = tid;
+        for (; i + 3u * kRankThreads < n4; i += 4u * kRankThreads) { // four loads in flight per thread
+            const float4 x0 = __ldg(p4 + i), x1 = __ldg(p4 + i + kRankThreads), x2 = __ldg(p4 + i + 2 * kRankThreads),
+                         x3 = __ldg(p4 + i + 3 * kRankThreads);
+            cnt += (x0.x > v) + (x0.y > v) + (x0.z > v) + (x0.w > v) + (x1.x > v) + (x1.y > v) + (x1.z > v) + (x1.w > v) +
+                   (x2.x > v) + (x2.y > v) + (x2.z > v) + (x2.w > v) + (x3.x > v) + (x3.y > v) + (x3.z > v) + (x3.w > v);
+        }
+        for (; i < n4; i += kRankThreads) {
+            const float4 x = __ldg(p4 + i);
+            cnt += (x.x > v) + (x.y > v) + (x.z > v) + (x.w > v);
+        }
+        for (uint32_t c = n4 * 4u + tid; c < n_vocab; c += kRankThreads)
+            cnt += __ldg(lrow + c) > v;
+    } else {
+        for (uint32_t c = tid; c < n_vocab; c += kRankThreads)
+            cnt += __ldg(lrow + c) > v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    if ((tid & 31u) == 0)
+        s_part[tid >> 5] = cnt;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t total = 0;
+        for (int w = 0; w < kRankThreads / 32; ++w)
+            total += s_part[w];
+        if (above) above[row] = total;
+        if (forced) forced[row] = (total < k) ? t : -1;
+    }
+}
+
+cudaError_t launch_rank_force(const float* logits, uint64_t ld, uint32_t batch, uint32_t n_vocab, const int32_t* token,
+                              uint32_t k, int32_t* forced, uint32_t* above, cudaStream_t stream)
+{
+    if (batch == 0)
+        return cudaSuccess;
+    rank_force_kernel<<<batch, kRankThreads, 0, stream>>>(logits, ld, n_vocab, token, k, forced, above);
+    return cudaGetLastError();
+}
+
 // ---- bookkeeping of one decode step (src/gen/session.cpp:416-444) ----------------------------------------------------
 __global__ void decode_commit_kernel(uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
                                      uint64_t history_ld, uint32_t history_cap, int32_t* history_len,

@@ -404,6 +404,18 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
     return MK_OK;
 }
 
+int mk_rank_force(mk_sampler* s, const float* logits, uint64_t ld, uint32_t batch, uint32_t n_vocab,
+                  const int32_t* token, uint32_t k, int32_t* forced, uint32_t* above, void* stream)
+{
+    if (!s || !logits || !token || (!forced && !above))
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_rank_force: logits, token and one output are required");
+    if (n_vocab == 0 || ld < n_vocab)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_rank_force: n_vocab %u, ld %llu", n_vocab, (unsigned long long)ld);
+    DeviceGuard g(s->device);
+    MK_CUDA(mk::launch_rank_force(logits, ld, batch, n_vocab, token, k, forced, above, (cudaStream_t)stream));
+    return MK_OK;
+}
+
 int mk_decode_commit(mk_sampler* s, uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
                      uint64_t history_ld, uint32_t history_cap, int32_t* history_len, int32_t* next_input,
                      int32_t* committed, uint32_t* flags, void* stream)

@@ -94,6 +94,9 @@ cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream);
 cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                                 int32_t* n_kept, int32_t* next_token, cudaStream_t stream);
 
+cudaError_t launch_rank_force(const float* logits, uint64_t ld, uint32_t batch, uint32_t n_vocab, const int32_t* token,
+                              uint32_t k, int32_t* forced, uint32_t* above, cudaStream_t stream);
+
 cudaError_t launch_decode_commit(uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
                                  uint64_t history_ld, uint32_t history_cap, int32_t* history_len, int32_t* next_input,
                                  int32_t* committed, uint32_t* flags, cudaStream_t stream);

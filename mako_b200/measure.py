@@ -113,6 +113,15 @@ def main():
     print(json.dumps(dict(config="3 rows overflowed", rows=flagged)), flush=True)
     del sets, s
 
+    # reasoning-budget logit test over the same 256 x 129280 rows (one streaming pass, 4 bytes per column)
+    v, b = 129280, 256
+    sets = _sets(4, b, v)
+    s = BatchSampler(v, b)
+    tok = torch.full((b,), 1234, dtype=torch.int32, device="cuda")
+    us = _time(lambda k: s.rank_force(sets[k % 4]["logits"], tok), args.steps)
+    report("rank test (is the token among the 3 largest), 256 x 129280", us, b, b * (4 * v + 12))
+    del sets, s
+
     # 4
     v, b, h, n_sh, k_sh = 151552, 1024, 4096, 8, 64
     sets = _sets(2, b, v, h)

@@ -220,6 +220,17 @@ class BatchSampler:
         return SampleResult(self.token[:b], self.prob[:b], self.flags[:b], self.n_cand[:b],
                             accepted=self.accepted[:b], draft_token=self.draft_token[:b])
 
+    def rank_force(self, logits: torch.Tensor, token: torch.Tensor, k: int = 3):
+        """ReasoningBudget::forced's logit test (src/server/openai.cpp:596-603) for every row: returns (forced [B]
+        int32: token[b] if fewer than k raw logits are greater than its own, else -1; above [B]: that count)."""
+        assert logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1
+        b, v = logits.shape
+        forced = torch.empty(b, dtype=torch.int32, device=self.device)
+        above = torch.empty(b, dtype=torch.int32, device=self.device)
+        check(lib.mk_rank_force(self._h, logits.data_ptr(), logits.stride(0), b, v, token.data_ptr(), k,
+                                forced.data_ptr(), above.data_ptr(), _stream_ptr(self.device)))
+        return forced, above
+
     def decode_commit(self, sampled: torch.Tensor, history: torch.Tensor, history_len: torch.Tensor, *, forced=None,
                       next_input=None, flags=None) -> torch.Tensor:
         """One decode step's bookkeeping on the device (src/gen/session.cpp:416-444): forced tokens replace sampled

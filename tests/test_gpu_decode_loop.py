@@ -66,3 +66,58 @@ def test_decode_commit_full_history_and_failed_rows(gpu_sampler_factory):
     assert hlen.cpu().tolist() == [1, 3, 2, 2]          # full row and failed row keep their length
     assert flags.cpu().tolist() == [0, 0x100, 0, 0]
     assert hist.cpu().numpy()[0, 0] == 5 and hist.cpu().numpy()[3, 1] == 8
+
+
+def rank_force_cpu(logits, token, k=3):
+    """ReasoningBudget::forced's logit test restated (src/server/openai.cpp:596-603): the loop counts logits strictly
+    greater than the token's and gives up at k."""
+    forced, above = [], []
+    for row, t in zip(logits, token):
+        if t < 0 or t >= row.shape[0]:
+            forced.append(-1)
+            above.append(-1)
+            continue
+        n = int((row > row[t]).sum())
+        above.append(n)
+        forced.append(int(t) if n < k else -1)
+    return forced, above
+
+
+def test_rank_force_known_answers_of_the_reference(gpu_sampler_factory):
+    """tests/server_test.cpp:139-153: all logits 0 and the closing token at 1 closes; three logits above it do not
+    close ("fourth is not closed early"); two above do ("third closes early")."""
+    import torch
+    nv, end = 4099, 4000
+    s = gpu_sampler_factory(nv, 4, 0)
+    rows = np.zeros((4, nv), dtype=np.float32)
+    rows[:, end] = 1.0
+    rows[1, :3] = 2.0
+    rows[2, :2] = 2.0
+    rows[3, 7] = np.nan                      # a NaN is never "greater"
+    token = np.array([end, end, end, end], dtype=np.int32)
+    forced, above = s.rank_force(torch.from_numpy(rows).cuda(), torch.from_numpy(token).cuda())
+    torch.cuda.synchronize()
+    assert forced.cpu().tolist() == [end, -1, end, end]
+    assert above.cpu().tolist() == [0, 3, 2, 0]
+
+
+def test_rank_force_random_rows(gpu_sampler_factory):
+    import torch
+    v, b = 129280, 12
+    s = gpu_sampler_factory(v, b, 0)
+    lg, spikes = synth.logits(77, b, v + 3, ld=v + 4)      # rows of v + 3 columns, 16-byte aligned
+    token = np.array([int(spikes[i, i % 8]) if i % 3 else (i * 9973) % v for i in range(b)], dtype=np.int32)
+    token[5], token[6] = -1, v + 3                          # no such token: nothing forced
+    d = torch.from_numpy(lg).cuda()
+    for view, nv in ((d[:, : v + 3], v + 3), (d[:, 1 : v + 2], v + 1)):   # aligned rows, then misaligned ones
+        forced, above = s.rank_force(view, torch.from_numpy(token).cuda(), k=3)
+        torch.cuda.synchronize()
+        wf, wa = rank_force_cpu(view.cpu().numpy(), token)
+        assert forced.cpu().tolist() == wf
+        assert above.cpu().tolist() == wa
+    # the forced tokens feed the commit step as they are
+    hist = torch.zeros((b, 4), dtype=torch.int32, device="cuda")
+    hlen = torch.zeros(b, dtype=torch.int32, device="cuda")
+    sampled = torch.full((b,), 11, dtype=torch.int32, device="cuda")
+    out = s.decode_commit(sampled, hist, hlen, forced=forced)
+    assert out.cpu().tolist() == [f if f >= 0 else 11 for f in wf]
