@@ -148,6 +148,19 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
 int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                     int32_t* n_kept, int32_t* next_token, void* stream);
 
+/* One step of the reference's drafter pick (ds_markov + ds_draft_pick, src/kernels/dsv41.metal:664-742; host loop
+ * src/dsv41/engine.cpp:1474-1497) for up to 8 sequences that share the drafter: per sequence b,
+ * score[v] = logits[b][v] + head[v] . embed[prev[b]] (head [n_vocab][rank], 16-byte aligned; embed [n_embed][rank]; rank a multiple of 4, <= 256),
+ * draft[b] = argmax_v score[v], the lowest id on ties (id 0 when no score is above -inf), and
+ * conf[b] = 1 / (1 + exp(-([x[b], embed[prev[b]]] . w))) with x [n_seq][x_ld] (dim used) and w [dim + rank].
+ * prev[b] is the previous draft of the chain (or the last sampled token at step 0); the caller runs the chain's steps
+ * one call after the other, as the reference does. The scores are not written anywhere. Floating point: dot products
+ * are summed in another order than the reference's simdgroup reduction — scores agree to about 1e-6 relative, so
+ * the argmax is the reference's unless the two best scores are that close. All pointers are device pointers. */
+int mk_draft_pick(mk_sampler* s, const float* logits, uint64_t ld, const float* head, const float* embed, const float* x,
+                  uint64_t x_ld, const float* w, const int32_t* prev, uint32_t n_seq, uint32_t n_vocab, uint32_t rank,
+                  uint32_t dim, uint32_t n_embed, int32_t* draft, float* conf, void* stream);
+
 /* The logit test of the reference's reasoning budget (ReasoningBudget::forced, src/server/openai.cpp:596-603): in
  * the budget's last stretch the closing token is forced as soon as it is among the k = 3 largest raw logits. Per row
  * b: above[b] = number of logits[b][i] strictly greater than logits[b][token[b]] (NaN never counts), forced[b] =

@@ -505,6 +505,153 @@ cudaError_t launch_rank_force(const float* logits, uint64_t ld, uint32_t batch, 
     return cudaGetLastError();
 }
 
+// ---- drafter pick (ds_markov + ds_draft_pick, src/kernels/dsv41.metal:664-742) ---------------------------------------
+// score[b][v] = logits[b][v] + head[v] . embed[prev[b]]; draft[b] = argmax_v score (lowest id on ties);
+// conf[b] = sigmoid([x[b], embed[prev[b]]] . w). The reference writes the scores to memory and picks in a second
+// kernel; here the scores never leave the registers: each warp keeps a head row in registers (rank / 32 floats per
+// lane), takes its dot product with every sequence's embedding row (shared memory) and folds it into a running best;
+// CTAs combine through one 64-bit atomic maximum per sequence on (order key of the score, ~id); the last CTA to
+// arrive writes the results: one launch per step. HBM-bound on the head
+// matrix: 4 * rank bytes per vocabulary row, read once for all sequences of the launch.
+constexpr int kPickThreads = 256, kPickMaxSeq = 8, kPickMaxRank = 256;
+
+template <int kSeq> // sequences the launch can carry: 1 (the reference's case, fewer registers) or kPickMaxSeq
+__global__ void __launch_bounds__(kPickThreads, kSeq == 1 ? 4 : 3) draft_score_kernel(const float* logits, uint64_t ld, const float* head,
+                                                                  const float* embed, const int32_t* prev,
+                                                                  uint32_t n_seq, uint32_t n_vocab, uint32_t rank,
+                                                                  uint32_t n_embed, unsigned long long* best,
+                                                                  const float* x, uint64_t x_ld, const float* w,
+                                                                  uint32_t dim, int32_t* draft, float* conf)
+{
+    __shared__ __align__(16) float s_e[kSeq][kPickMaxRank];
+    __shared__ unsigned long long s_best[kSeq];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t i = tid; i < n_seq * kPickMaxRank; i += kPickThreads) {
+        const uint32_t b = i / kPickMaxRank, j = i - b * kPickMaxRank;
+        const int32_t p = prev[b];
+        s_e[b][j] = (j < rank && p >= 0 && (uint32_t)p < n_embed) ? __ldg(embed + (size_t)p * rank + j) : 0.0f;
+    }
+    if (tid < kSeq)
+        s_best[tid] = 0ull;
+    __syncthreads();
+    unsigned long long mine[kSeq];
+#pragma unroll
+    for (int b = 0; b < kSeq; ++b)
+        mine[b] = 0ull;
+    // Four head rows per warp and trip, each lane 2 x 4 consecutive floats of a row (128-bit loads; rank a multiple
+    // of 4, the rest of a shorter rank reads as zero): 4 KB in flight per warp.
+    constexpr uint32_t kRows = 4;
+    const uint32_t warps = gridDim.x * (kPickThreads / 32);
+    for (uint32_t v0 = (blockIdx.x * (kPickThreads / 32) + warp) * kRows; v0 < n_vocab; v0 += warps * kRows) {
+        float4 h[kRows][2];
+#pragma unroll
+        for (uint32_t r = 0; r < kRows; ++r)
+#pragma unroll
+            for (uint32_t k = 0; k < 2; ++k) {
+                const uint32_t i = 4u * lane + 128u * k;
+                h[r][k] = (v0 + r < n_vocab && i < rank)
+                              ? __ldg(reinterpret_cast<const float4*>(head + (size_t)(v0 + r) * rank + i))
+                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+        for (int b = 0; b < kSeq; ++b) {
+            if ((uint32_t)b >= n_seq)
+                break;
+            const float4 e0 = *reinterpret_cast<const float4*>(&s_e[b][4u * lane]);
+            const float4 e1 = *reinterpret_cast<const float4*>(&s_e[b][4u * lane + 128u]);
+#pragma unroll
+            for (uint32_t r = 0; r < kRows; ++r) {
+                float acc = h[r][0].x * e0.x;
+                acc = fmaf(h[r][0].y, e0.y, acc);
+                acc = fmaf(h[r][0].z, e0.z, acc);
+                acc = fmaf(h[r][0].w, e0.w, acc);
+                acc = fmaf(h[r][1].x, e1.x, acc);
+                acc = fmaf(h[r][1].y, e1.y, acc);
+                acc = fmaf(h[r][1].z, e1.z, acc);
+                acc = fmaf(h[r][1].w, e1.w, acc);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+                    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                const uint32_t v = v0 + r;
+                if (v < n_vocab) {
+                    const float sc = __ldg(logits + (size_t)b * ld + v) + acc;
+                    // larger score wins, then the lower id: the id enters complemented; NaN and -inf never win
+                    // (`s > bv` from bv = -inf in the reference): key 0
+                    const unsigned long long key = (sc > -__int_as_float(0x7f800000))
+                                                       ? (((unsigned long long)order_key(sc) << 32) | (0xffffffffu - v))
+                                                       : 0ull;
+                    mine[b] = max(mine[b], key);
+                }
+            }
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int b = 0; b < kSeq; ++b)
+            if ((uint32_t)b < n_seq && mine[b])
+                atomicMax(&s_best[b], mine[b]);
+    }
+    __syncthreads();
+    if (tid < n_seq && s_best[tid])
+        atomicMax(&best[tid], s_best[tid]);
+    // The CTA that arrives last (a ticket counter behind the maxima) has every CTA's maximum in front of it: it
+    // writes the drafts and the confidences (ds_draft_pick's second half) and leaves maxima and counter clear for the
+    // next call.
+    __shared__ uint32_t s_last;
+    __shared__ float s_part[kPickThreads / 32];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0)
+        s_last = atomicAdd(reinterpret_cast<unsigned int*>(best + kPickMaxSeq), 1u) == gridDim.x - 1u;
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    for (uint32_t b = 0; b < n_seq; ++b) {
+        float d = 0.0f;
+        for (uint32_t i = tid; i < dim + rank; i += kPickThreads)
+            d = fmaf(__ldg(w + i), i < dim ? __ldg(x + (size_t)b * x_ld + i) : s_e[b][i - dim], d);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (lane == 0)
+            s_part[warp] = d;
+        __syncthreads();
+        if (tid == 0) {
+            float sum = 0.0f;
+            for (int k = 0; k < kPickThreads / 32; ++k)
+                sum += s_part[k];
+            const unsigned long long key = *(volatile unsigned long long*)&best[b];
+            best[b] = 0ull;
+            draft[b] = key ? (int32_t)(0xffffffffu - (uint32_t)(key & 0xffffffffull)) : 0; // nothing comparable: id 0
+            conf[b] = 1.0f / (1.0f + expf(-sum));
+        }
+        __syncthreads();
+    }
+    if (tid == 0)
+        *reinterpret_cast<unsigned int*>(best + kPickMaxSeq) = 0u;
+}
+
+cudaError_t launch_draft_pick(const float* logits, uint64_t ld, const float* head, const float* embed, const float* x,
+                              uint64_t x_ld, const float* w, const int32_t* prev, uint32_t n_seq, uint32_t n_vocab,
+                              uint32_t rank, uint32_t dim, uint32_t n_embed, unsigned long long* best, int32_t* draft,
+                              float* conf, cudaStream_t stream)
+{
+    if (n_seq == 0)
+        return cudaSuccess;
+    // `best` (the maxima, then the ticket counter) is zero on entry: the handle clears it once and the kernel's last
+    // CTA clears what it has read
+    const uint32_t rows_per_trip = (kPickThreads / 32) * 4;
+    const uint32_t grid = min((n_vocab + rows_per_trip - 1) / rows_per_trip, 148u * 4u); // persistent, grid-stride
+    if (n_seq == 1)
+        draft_score_kernel<1><<<grid, kPickThreads, 0, stream>>>(logits, ld, head, embed, prev, n_seq, n_vocab, rank,
+                                                                n_embed, best, x, x_ld, w, dim, draft, conf);
+    else
+        draft_score_kernel<kPickMaxSeq><<<grid, kPickThreads, 0, stream>>>(logits, ld, head, embed, prev, n_seq, n_vocab,
+                                                                          rank, n_embed, best, x, x_ld, w, dim, draft, conf);
+    return cudaGetLastError();
+}
+
 // ---- bookkeeping of one decode step (src/gen/session.cpp:416-444) ----------------------------------------------------
 __global__ void decode_commit_kernel(uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
                                      uint64_t history_ld, uint32_t history_cap, int32_t* history_len,

@@ -57,6 +57,7 @@ struct mk_sampler {
     // host-buffer staging (sized on first use)
     cudaStream_t own_stream = nullptr;
     unsigned long long* timing = nullptr; // debug: per-row phase timestamps of the next launches
+    unsigned long long* pick_best = nullptr; // mk_draft_pick: one packed (score, id) maximum per sequence
     unsigned char* stage = nullptr;
     size_t stage_bytes = 0;
 };
@@ -235,6 +236,9 @@ int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t m
     alloc((void**)&s->p_flags, b * 4);
     alloc((void**)&s->q_flags, b * 4);
     alloc((void**)&s->p_tok, b * 4);
+    alloc((void**)&s->pick_best, (mk::kDraftPickMaxSeq + 1) * sizeof(unsigned long long)); // maxima + ticket counter
+    if (e == cudaSuccess)
+        e = cudaMemset(s->pick_best, 0, (mk::kDraftPickMaxSeq + 1) * sizeof(unsigned long long));
     if (e == cudaSuccess)
         e = cudaStreamCreateWithFlags(&s->own_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) {
@@ -251,7 +255,7 @@ void mk_sampler_destroy(mk_sampler* s)
         return;
     DeviceGuard g(s->device);
     void* ptrs[] = {s->scratch, s->p_ids, s->q_ids, s->p_q, s->q_q, s->p_total, s->q_total, s->q_prob,
-                    s->p_n,     s->q_n,   s->p_flags, s->q_flags, s->p_tok, s->stage};
+                    s->p_n,     s->q_n,   s->p_flags, s->q_flags, s->p_tok, s->stage, s->pick_best};
     for (void* p : ptrs)
         if (p)
             cudaFree(p);
@@ -401,6 +405,23 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
     r.u_accept = u_accept; r.u_resample = u_resample;
     r.accepted = accepted; r.token = token; r.flags = flags;
     MK_CUDA(mk::launch_pq_resolve(r, st));
+    return MK_OK;
+}
+
+int mk_draft_pick(mk_sampler* s, const float* logits, uint64_t ld, const float* head, const float* embed, const float* x,
+                  uint64_t x_ld, const float* w, const int32_t* prev, uint32_t n_seq, uint32_t n_vocab, uint32_t rank,
+                  uint32_t dim, uint32_t n_embed, int32_t* draft, float* conf, void* stream)
+{
+    if (!s || !logits || !head || !embed || !x || !w || !prev || !draft || !conf)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_draft_pick: null argument");
+    if (n_seq > mk::kDraftPickMaxSeq || rank == 0 || rank > mk::kDraftPickMaxRank || (rank & 3u) != 0 ||
+        (reinterpret_cast<uintptr_t>(head) & 15u) != 0 || n_vocab == 0 || ld < n_vocab ||
+        x_ld < dim)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_draft_pick: n_seq %u (max %u), rank %u (a multiple of 4, max %u; head 16-byte aligned), n_vocab %u, ld %llu",
+                    n_seq, mk::kDraftPickMaxSeq, rank, mk::kDraftPickMaxRank, n_vocab, (unsigned long long)ld);
+    DeviceGuard g(s->device);
+    MK_CUDA(mk::launch_draft_pick(logits, ld, head, embed, x, x_ld, w, prev, n_seq, n_vocab, rank, dim, n_embed,
+                                  s->pick_best, draft, conf, (cudaStream_t)stream));
     return MK_OK;
 }
 

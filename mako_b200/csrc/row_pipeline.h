@@ -94,6 +94,12 @@ cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream);
 cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                                 int32_t* n_kept, int32_t* next_token, cudaStream_t stream);
 
+constexpr uint32_t kDraftPickMaxSeq = 8, kDraftPickMaxRank = 256;
+cudaError_t launch_draft_pick(const float* logits, uint64_t ld, const float* head, const float* embed, const float* x,
+                              uint64_t x_ld, const float* w, const int32_t* prev, uint32_t n_seq, uint32_t n_vocab,
+                              uint32_t rank, uint32_t dim, uint32_t n_embed, unsigned long long* best, int32_t* draft,
+                              float* conf, cudaStream_t stream);
+
 cudaError_t launch_rank_force(const float* logits, uint64_t ld, uint32_t batch, uint32_t n_vocab, const int32_t* token,
                               uint32_t k, int32_t* forced, uint32_t* above, cudaStream_t stream);
 

@@ -122,6 +122,22 @@ def main():
     report("rank test (is the token among the 3 largest), 256 x 129280", us, b, b * (4 * v + 12))
     del sets, s
 
+    # drafter pick: logits + head . embed[prev] -> argmax, confidence; head 129280 x 256 fp32 read once per step
+    v, rank, dim = 129280, 256, 4096
+    g = torch.Generator(device="cuda").manual_seed(SEED)
+    head = torch.randn((v, rank), generator=g, device="cuda") * 0.05
+    embed = torch.randn((v, rank), generator=g, device="cuda")
+    w = torch.randn(dim + rank, generator=g, device="cuda") * 0.05
+    s = BatchSampler(v, 8)
+    for n_seq in (1, 8):
+        lg = torch.randn((n_seq, v), generator=g, device="cuda") * 2
+        x = torch.randn((n_seq, dim), generator=g, device="cuda")
+        prev = torch.arange(n_seq, dtype=torch.int32, device="cuda") * 1000 + 5
+        us = _time(lambda k: s.draft_pick(lg, head, embed, x, w, prev), args.steps)
+        print(json.dumps(dict(config=f"drafter pick, {n_seq} sequence(s), head 129280 x 256", us_per_step=round(us, 2),
+                              effective_gbs=round((4 * v * rank + n_seq * 4 * v) / us / 1e3, 1))), flush=True)
+    del head, embed, s
+
     # 4
     v, b, h, n_sh, k_sh = 151552, 1024, 4096, 8, 64
     sets = _sets(2, b, v, h)

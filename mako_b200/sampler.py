@@ -220,6 +220,23 @@ class BatchSampler:
         return SampleResult(self.token[:b], self.prob[:b], self.flags[:b], self.n_cand[:b],
                             accepted=self.accepted[:b], draft_token=self.draft_token[:b])
 
+    def draft_pick(self, logits, head, embed, x, w, prev):
+        """One step of the drafter pick (src/kernels/dsv41.metal:664-742) for up to 8 sequences: logits [S, V],
+        head [V, rank], embed [E, rank], x [S, dim], w [dim + rank], prev [S] int32. Returns (draft [S] int32,
+        conf [S] float32)."""
+        for t in (logits, head, embed, x, w):
+            assert t.is_cuda and t.dtype == torch.float32 and t.stride(-1) == 1
+        assert head.is_contiguous() and embed.is_contiguous() and w.is_contiguous()
+        n_seq, v = logits.shape
+        rank, dim = head.shape[1], x.shape[1]
+        assert head.shape[0] == v and embed.shape[1] == rank and w.numel() == dim + rank
+        draft = torch.empty(n_seq, dtype=torch.int32, device=self.device)
+        conf = torch.empty(n_seq, dtype=torch.float32, device=self.device)
+        check(lib.mk_draft_pick(self._h, logits.data_ptr(), logits.stride(0), head.data_ptr(), embed.data_ptr(),
+                                x.data_ptr(), x.stride(0), w.data_ptr(), prev.data_ptr(), n_seq, v, rank, dim,
+                                embed.shape[0], draft.data_ptr(), conf.data_ptr(), _stream_ptr(self.device)))
+        return draft, conf
+
     def rank_force(self, logits: torch.Tensor, token: torch.Tensor, k: int = 3):
         """ReasoningBudget::forced's logit test (src/server/openai.cpp:596-603) for every row: returns (forced [B]
         int32: token[b] if fewer than k raw logits are greater than its own, else -1; above [B]: that count)."""
