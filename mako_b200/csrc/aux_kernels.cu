@@ -526,18 +526,15 @@ __global__ void __launch_bounds__(kPickThreads, kSeq == 1 ? 4 : 3) draft_score_k
     __shared__ __align__(16) float s_e[kSeq][kPickMaxRank];
     __shared__ unsigned long long s_best[kSeq];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    for (uint32_t i = tid; i < n_seq * kPickMaxRank; i += kPickThreads) {
+    for (uint32_t i = tid; i < (uint32_t)kSeq * kPickMaxRank; i += kPickThreads) {
         const uint32_t b = i / kPickMaxRank, j = i - b * kPickMaxRank;
-        const int32_t p = prev[b];
+        const int32_t p = (b < n_seq) ? prev[b] : -1;
         s_e[b][j] = (j < rank && p >= 0 && (uint32_t)p < n_embed) ? __ldg(embed + (size_t)p * rank + j) : 0.0f;
     }
     if (tid < kSeq)
         s_best[tid] = 0ull;
     __syncthreads();
-    unsigned long long mine[kSeq];
-#pragma unroll
-    for (int b = 0; b < kSeq; ++b)
-        mine[b] = 0ull;
+    unsigned long long mine[1] = {0ull}; // running best: of the one sequence, or of this lane's sequence (lane / 4)
     // Four head rows per warp and trip, each lane 2 x 4 consecutive floats of a row (128-bit loads; rank a multiple
     // of 4, the rest of a shorter rank reads as zero): 4 KB in flight per warp.
     constexpr uint32_t kRows = 4;
@@ -553,43 +550,90 @@ __global__ void __launch_bounds__(kPickThreads, kSeq == 1 ? 4 : 3) draft_score_k
                               ? __ldg(reinterpret_cast<const float4*>(head + (size_t)(v0 + r) * rank + i))
                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
-#pragma unroll
-        for (int b = 0; b < kSeq; ++b) {
-            if ((uint32_t)b >= n_seq)
-                break;
-            const float4 e0 = *reinterpret_cast<const float4*>(&s_e[b][4u * lane]);
-            const float4 e1 = *reinterpret_cast<const float4*>(&s_e[b][4u * lane + 128u]);
-#pragma unroll
-            for (uint32_t r = 0; r < kRows; ++r) {
-                float acc = h[r][0].x * e0.x;
-                acc = fmaf(h[r][0].y, e0.y, acc);
-                acc = fmaf(h[r][0].z, e0.z, acc);
-                acc = fmaf(h[r][0].w, e0.w, acc);
-                acc = fmaf(h[r][1].x, e1.x, acc);
-                acc = fmaf(h[r][1].y, e1.y, acc);
-                acc = fmaf(h[r][1].z, e1.z, acc);
-                acc = fmaf(h[r][1].w, e1.w, acc);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
-                    acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                const uint32_t v = v0 + r;
-                if (v < n_vocab) {
-                    const float sc = __ldg(logits + (size_t)b * ld + v) + acc;
-                    // larger score wins, then the lower id: the id enters complemented; NaN and -inf never win
-                    // (`s > bv` from bv = -inf in the reference): key 0
-                    const unsigned long long key = (sc > -__int_as_float(0x7f800000))
-                                                       ? (((unsigned long long)order_key(sc) << 32) | (0xffffffffu - v))
-                                                       : 0ull;
-                    mine[b] = max(mine[b], key);
+        if constexpr (kSeq == 1) {
+    #pragma unroll
+            for (int b = 0; b < kSeq; ++b) {
+                if ((uint32_t)b >= n_seq)
+                    break;
+                const float4 e0 = *reinterpret_cast<const float4*>(&s_e[b][4u * lane]);
+                const float4 e1 = *reinterpret_cast<const float4*>(&s_e[b][4u * lane + 128u]);
+    #pragma unroll
+                for (uint32_t r = 0; r < kRows; ++r) {
+                    float acc = h[r][0].x * e0.x;
+                    acc = fmaf(h[r][0].y, e0.y, acc);
+                    acc = fmaf(h[r][0].z, e0.z, acc);
+                    acc = fmaf(h[r][0].w, e0.w, acc);
+                    acc = fmaf(h[r][1].x, e1.x, acc);
+                    acc = fmaf(h[r][1].y, e1.y, acc);
+                    acc = fmaf(h[r][1].z, e1.z, acc);
+                    acc = fmaf(h[r][1].w, e1.w, acc);
+    #pragma unroll
+                    for (int o = 16; o > 0; o >>= 1)
+                        acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    const uint32_t v = v0 + r;
+                    if (v < n_vocab) {
+                        const float sc = __ldg(logits + (size_t)b * ld + v) + acc;
+                        // larger score wins, then the lower id: the id enters complemented; NaN and -inf never win
+                        // (`s > bv` from bv = -inf in the reference): key 0
+                        const unsigned long long key = (sc > -__int_as_float(0x7f800000))
+                                                           ? (((unsigned long long)order_key(sc) << 32) | (0xffffffffu - v))
+                                                           : 0ull;
+                        mine[b] = max(mine[b], key);
+                    }
                 }
+            }
+        } else {
+            // 4 rows x 8 sequences = 32 dot products per trip: every lane forms its share of all 32, then a butterfly
+            // that halves the number of values a lane holds at each of its five steps (31 shuffles instead of 160)
+            // leaves lane l with the total of product l = sequence l / 4, row l % 4.
+            static_assert(kSeq == 8 && kRows == 4, "the butterfly below is written for 32 products");
+            float acc[32];
+#pragma unroll
+            for (int q = 0; q < kSeq; ++q) {
+                const float4 e0 = *reinterpret_cast<const float4*>(&s_e[q][4u * lane]);
+                const float4 e1 = *reinterpret_cast<const float4*>(&s_e[q][4u * lane + 128u]);
+#pragma unroll
+                for (uint32_t r = 0; r < kRows; ++r) {
+                    float t = h[r][0].x * e0.x;
+                    t = fmaf(h[r][0].y, e0.y, t);
+                    t = fmaf(h[r][0].z, e0.z, t);
+                    t = fmaf(h[r][0].w, e0.w, t);
+                    t = fmaf(h[r][1].x, e1.x, t);
+                    t = fmaf(h[r][1].y, e1.y, t);
+                    t = fmaf(h[r][1].z, e1.z, t);
+                    t = fmaf(h[r][1].w, e1.w, t);
+                    acc[q * 4 + (int)r] = t;
+                }
+            }
+#pragma unroll
+            for (int half = 16; half > 0; half >>= 1) {
+                const bool upper = (lane & (uint32_t)half) != 0;
+#pragma unroll
+                for (int i = 0; i < half; ++i) {
+                    const float send = upper ? acc[i] : acc[i + half];
+                    const float keep = upper ? acc[i + half] : acc[i];
+                    acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+                }
+            }
+            const uint32_t q = lane >> 2, v = v0 + (lane & 3u);
+            if (q < n_seq && v < n_vocab) {
+                const float sc = __ldg(logits + (size_t)q * ld + v) + acc[0];
+                const unsigned long long key = (sc > -__int_as_float(0x7f800000))
+                                                   ? (((unsigned long long)order_key(sc) << 32) | (0xffffffffu - v))
+                                                   : 0ull;
+                mine[0] = max(mine[0], key); // this lane's sequence is lane / 4
             }
         }
     }
-    if (lane == 0) {
-#pragma unroll
-        for (int b = 0; b < kSeq; ++b)
-            if ((uint32_t)b < n_seq && mine[b])
-                atomicMax(&s_best[b], mine[b]);
+    if constexpr (kSeq == 1) {
+        if (lane == 0 && mine[0])
+            atomicMax(&s_best[0], mine[0]);
+    } else {
+        unsigned long long m = mine[0]; // lanes 4q .. 4q+3 hold sequence q
+        m = max(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = max(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        if ((lane & 3u) == 0 && (lane >> 2) < n_seq && m)
+            atomicMax(&s_best[lane >> 2], m);
     }
     __syncthreads();
     if (tid < n_seq && s_best[tid])
