@@ -161,6 +161,14 @@ int mk_draft_pick(mk_sampler* s, const float* logits, uint64_t ld, const float* 
                   uint64_t x_ld, const float* w, const int32_t* prev, uint32_t n_seq, uint32_t n_vocab, uint32_t rank,
                   uint32_t dim, uint32_t n_embed, int32_t* draft, float* conf, void* stream);
 
+/* The reference's other drafter pick (hy4_draft_pick, src/kernels/hy4f.metal:352-397), per sequence b:
+ * draft[b] = index of the largest logit (the lowest index on ties; 0 when nothing is above -inf), also written to
+ * next_prev[b] (optional: the next step's embedding index), conf[b] = 1 / (1 + exp(-(conf_w . h[b] + conf_bias)))
+ * over `width` floats. logits [n_seq][ld], h [n_seq][h_ld]. All pointers are device pointers. */
+int mk_draft_pick_plain(mk_sampler* s, const float* logits, uint64_t ld, uint32_t n_seq, uint32_t n_vocab, const float* h,
+                        uint64_t h_ld, const float* conf_w, uint32_t width, float conf_bias, int32_t* draft, float* conf,
+                        int32_t* next_prev, void* stream);
+
 /* The logit test of the reference's reasoning budget (ReasoningBudget::forced, src/server/openai.cpp:596-603): in
  * the budget's last stretch the closing token is forced as soon as it is among the k = 3 largest raw logits. Per row
  * b: above[b] = number of logits[b][i] strictly greater than logits[b][token[b]] (NaN never counts), forced[b] =

@@ -104,6 +104,8 @@ def _load() -> C.CDLL:
     lib.mk_spec_resolve.argtypes = [vp, C.c_uint32, C.c_uint32, vp, vp, vp, vp, vp]
     lib.mk_draft_pick.argtypes = [vp, vp, C.c_uint64, vp, vp, vp, C.c_uint64, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32,
                                   C.c_uint32, C.c_uint32, vp, vp, vp]
+    lib.mk_draft_pick_plain.argtypes = [vp, vp, C.c_uint64, C.c_uint32, C.c_uint32, vp, C.c_uint64, vp, C.c_uint32,
+                                        C.c_float, vp, vp, vp, vp]
     lib.mk_rank_force.argtypes = [vp, vp, C.c_uint64, C.c_uint32, C.c_uint32, vp, C.c_uint32, vp, vp, vp]
     lib.mk_decode_commit.argtypes = [vp, C.c_uint32, vp, vp, vp, C.c_uint64, C.c_uint32, vp, vp, vp, vp, vp]
     lib.mk_vp_record_bytes.restype = C.c_uint32

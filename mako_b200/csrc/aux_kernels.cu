@@ -696,6 +696,81 @@ cudaError_t launch_draft_pick(const float* logits, uint64_t ld, const float* hea
     return cudaGetLastError();
 }
 
+// ---- plain drafter pick (hy4_draft_pick, src/kernels/hy4f.metal:352-397) ------------------------------------------------
+// draft = the largest logit (the lowest index on ties; 0 when nothing is above -inf), conf = sigmoid(conf_w . h + bias).
+// One CTA per sequence, as the reference has one threadgroup: a latency kernel over one 0.5 MB row.
+constexpr int kPlainPickThreads = 1024;
+__global__ void __launch_bounds__(kPlainPickThreads) draft_pick_plain_kernel(const float* logits, uint64_t ld,
+                                                                            uint32_t n_vocab, const float* h,
+                                                                            uint64_t h_ld, const float* conf_w,
+                                                                            uint32_t width, float conf_bias,
+                                                                            int32_t* draft, float* conf, int32_t* next_prev)
+{
+    __shared__ unsigned long long s_key[kPlainPickThreads / 32];
+    __shared__ float s_dot[kPlainPickThreads / 32];
+    const uint32_t b = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const float* lrow = logits + (size_t)b * ld;
+    const float ninf = -__int_as_float(0x7f800000);
+    unsigned long long key = 0ull; // (order key of the value, ~index): the larger value, then the lower index
+    auto take = [&](float v, uint32_t i) {
+        if (v > ninf)
+            key = max(key, ((unsigned long long)order_key(v) << 32) | (0xffffffffu - i));
+    };
+    if ((reinterpret_cast<uintptr_t>(lrow) & 15u) == 0) {
+        const float4* p4 = reinterpret_cast<const float4*>(lrow);
+        const uint32_t n4 = n_vocab / 4u;
+        for (uint32_t i = tid; i < n4; i += kPlainPickThreads) {
+            const float4 x = __ldg(p4 + i);
+            take(x.x, 4u * i);
+            take(x.y, 4u * i + 1u);
+            take(x.z, 4u * i + 2u);
+            take(x.w, 4u * i + 3u);
+        }
+        for (uint32_t c = n4 * 4u + tid; c < n_vocab; c += kPlainPickThreads)
+            take(__ldg(lrow + c), c);
+    } else {
+        for (uint32_t c = tid; c < n_vocab; c += kPlainPickThreads)
+            take(__ldg(lrow + c), c);
+    }
+    float d = 0.0f;
+    for (uint32_t i = tid; i < width; i += kPlainPickThreads)
+        d = fmaf(__ldg(conf_w + i), __ldg(h + (size_t)b * h_ld + i), d);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        key = max(key, __shfl_xor_sync(0xffffffffu, key, o));
+        d += __shfl_xor_sync(0xffffffffu, d, o);
+    }
+    if (lane == 0) {
+        s_key[warp] = key;
+        s_dot[warp] = d;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        unsigned long long k = 0ull;
+        float sum = 0.0f;
+        for (int i = 0; i < kPlainPickThreads / 32; ++i) {
+            k = max(k, s_key[i]);
+            sum += s_dot[i];
+        }
+        const int32_t id = k ? (int32_t)(0xffffffffu - (uint32_t)(k & 0xffffffffull)) : 0;
+        draft[b] = id;
+        if (next_prev)
+            next_prev[b] = id;
+        conf[b] = 1.0f / (1.0f + expf(-(sum + conf_bias)));
+    }
+}
+
+cudaError_t launch_draft_pick_plain(const float* logits, uint64_t ld, uint32_t n_seq, uint32_t n_vocab, const float* h,
+                                    uint64_t h_ld, const float* conf_w, uint32_t width, float conf_bias, int32_t* draft,
+                                    float* conf, int32_t* next_prev, cudaStream_t stream)
+{
+    if (n_seq == 0)
+        return cudaSuccess;
+    draft_pick_plain_kernel<<<n_seq, kPlainPickThreads, 0, stream>>>(logits, ld, n_vocab, h, h_ld, conf_w, width,
+                                                                    conf_bias, draft, conf, next_prev);
+    return cudaGetLastError();
+}
+
 // ---- bookkeeping of one decode step (src/gen/session.cpp:416-444) ----------------------------------------------------
 __global__ void decode_commit_kernel(uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
                                      uint64_t history_ld, uint32_t history_cap, int32_t* history_len,

@@ -425,6 +425,21 @@ int mk_draft_pick(mk_sampler* s, const float* logits, uint64_t ld, const float* 
     return MK_OK;
 }
 
+int mk_draft_pick_plain(mk_sampler* s, const float* logits, uint64_t ld, uint32_t n_seq, uint32_t n_vocab, const float* h,
+                        uint64_t h_ld, const float* conf_w, uint32_t width, float conf_bias, int32_t* draft, float* conf,
+                        int32_t* next_prev, void* stream)
+{
+    if (!s || !logits || !h || !conf_w || !draft || !conf)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_draft_pick_plain: null argument");
+    if (n_vocab == 0 || ld < n_vocab || h_ld < width)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_draft_pick_plain: n_vocab %u, ld %llu, width %u, h_ld %llu", n_vocab,
+                    (unsigned long long)ld, width, (unsigned long long)h_ld);
+    DeviceGuard g(s->device);
+    MK_CUDA(mk::launch_draft_pick_plain(logits, ld, n_seq, n_vocab, h, h_ld, conf_w, width, conf_bias, draft, conf,
+                                        next_prev, (cudaStream_t)stream));
+    return MK_OK;
+}
+
 int mk_rank_force(mk_sampler* s, const float* logits, uint64_t ld, uint32_t batch, uint32_t n_vocab,
                   const int32_t* token, uint32_t k, int32_t* forced, uint32_t* above, void* stream)
 {

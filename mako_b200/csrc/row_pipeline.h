@@ -100,6 +100,10 @@ cudaError_t launch_draft_pick(const float* logits, uint64_t ld, const float* hea
                               uint32_t rank, uint32_t dim, uint32_t n_embed, unsigned long long* best, int32_t* draft,
                               float* conf, cudaStream_t stream);
 
+cudaError_t launch_draft_pick_plain(const float* logits, uint64_t ld, uint32_t n_seq, uint32_t n_vocab, const float* h,
+                                    uint64_t h_ld, const float* conf_w, uint32_t width, float conf_bias, int32_t* draft,
+                                    float* conf, int32_t* next_prev, cudaStream_t stream);
+
 cudaError_t launch_rank_force(const float* logits, uint64_t ld, uint32_t batch, uint32_t n_vocab, const int32_t* token,
                               uint32_t k, int32_t* forced, uint32_t* above, cudaStream_t stream);
 

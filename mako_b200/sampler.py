@@ -237,6 +237,19 @@ class BatchSampler:
                                 embed.shape[0], draft.data_ptr(), conf.data_ptr(), _stream_ptr(self.device)))
         return draft, conf
 
+    def draft_pick_plain(self, logits, h, conf_w, conf_bias: float, next_prev=None):
+        """hy4_draft_pick (src/kernels/hy4f.metal:352-397): (argmax of each row with the lowest index on ties,
+        sigmoid(conf_w . h[b] + conf_bias)). logits [S, V], h [S, width], conf_w [width]."""
+        for t in (logits, h, conf_w):
+            assert t.is_cuda and t.dtype == torch.float32 and t.stride(-1) == 1
+        n_seq, v = logits.shape
+        draft = torch.empty(n_seq, dtype=torch.int32, device=self.device)
+        conf = torch.empty(n_seq, dtype=torch.float32, device=self.device)
+        check(lib.mk_draft_pick_plain(self._h, logits.data_ptr(), logits.stride(0), n_seq, v, h.data_ptr(), h.stride(0),
+                                      conf_w.data_ptr(), conf_w.numel(), float(conf_bias), draft.data_ptr(),
+                                      conf.data_ptr(), _ptr(next_prev), _stream_ptr(self.device)))
+        return draft, conf
+
     def rank_force(self, logits: torch.Tensor, token: torch.Tensor, k: int = 3):
         """ReasoningBudget::forced's logit test (src/server/openai.cpp:596-603) for every row: returns (forced [B]
         int32: token[b] if fewer than k raw logits are greater than its own, else -1; above [B]: that count)."""

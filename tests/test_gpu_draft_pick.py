@@ -73,3 +73,32 @@ def test_draft_pick_ties_and_non_finite(gpu_sampler_factory):
     torch.cuda.synchronize()
     assert draft.cpu().tolist() == [70, 0, 4500, 5002]
     assert conf.cpu().tolist() == [0.5, 0.5, 0.5, 0.5]
+
+
+def test_draft_pick_plain(gpu_sampler_factory):
+    """hy4_draft_pick (src/kernels/hy4f.metal:352-397): the largest logit with the lowest index on ties, confidence =
+    sigmoid(conf_w . h + bias); the argmax is exact, the confidence a float dot product (tolerance)."""
+    import torch
+    v, width, n = 129283, 4096, 6
+    rng = np.random.default_rng(3)
+    logits = rng.normal(0, 2, size=(n, v)).astype(np.float32)
+    logits[1, [90000, 17, 4000]] = 50.0          # ties: 17
+    logits[2, :] = -np.inf                       # nothing above -inf: 0
+    logits[3, 5] = np.nan
+    logits[4, v - 1] = 60.0                      # the last column
+    h = rng.normal(0, 1, size=(n, width)).astype(np.float32)
+    w = rng.normal(0, 0.02, size=width).astype(np.float32)
+    s = gpu_sampler_factory(v, 8, 0)
+    nxt = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+    logits = np.ascontiguousarray(logits)        # row stride v floats: only row 0 is 16-byte aligned
+    draft, conf = s.draft_pick_plain(torch.from_numpy(logits).cuda(), torch.from_numpy(h).cuda(),
+                                     torch.from_numpy(w).cuda(), 0.25, next_prev=nxt)
+    torch.cuda.synchronize()
+    want = []
+    for b in range(n):
+        row = np.where(np.isnan(logits[b]), -np.inf, logits[b])
+        want.append(int(np.argmax(row)) if np.isfinite(row).any() or (row == np.inf).any() else 0)
+    assert draft.cpu().tolist() == want
+    assert nxt.cpu().tolist() == want
+    wc = 1.0 / (1.0 + np.exp(-(h.astype(np.float64) @ w.astype(np.float64) + 0.25)))
+    assert np.allclose(conf.cpu().numpy(), wc, rtol=2e-6, atol=2e-7)
