@@ -156,7 +156,8 @@ int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t
  * prev[b] is the previous draft of the chain (or the last sampled token at step 0); the caller runs the chain's steps
  * one call after the other, as the reference does. The scores are not written anywhere. Floating point: dot products
  * are summed in another order than the reference's simdgroup reduction — scores agree to about 1e-6 relative, so
- * the argmax is the reference's unless the two best scores are that close. All pointers are device pointers. */
+ * the argmax is the reference's unless the two best scores are that close. All pointers are device pointers. Calls on
+ * one handle must not overlap (they share the handle's maxima and ticket counter); use one handle per stream. */
 int mk_draft_pick(mk_sampler* s, const float* logits, uint64_t ld, const float* head, const float* embed, const float* x,
                   uint64_t x_ld, const float* w, const int32_t* prev, uint32_t n_seq, uint32_t n_vocab, uint32_t rank,
                   uint32_t dim, uint32_t n_embed, int32_t* draft, float* conf, void* stream);
