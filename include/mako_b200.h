@@ -39,7 +39,8 @@ typedef enum mk_status {
 #define MK_FLAG_OVERFLOW          0x010u /* more candidates than the handle's capacity: token = -1 */
 #define MK_FLAG_VP_TRUNCATED      0x020u /* vocab-parallel: the nucleus may reach past a shard's top-k list */
 #define MK_FLAG_TIMEOUT           0x040u /* a bounded device-side wait ran out: token = -1 */
-#define MK_FLAG_HISTORY_FULL      0x100u /* mk_decode_commit: the row's history buffer is full, the token was not appended */
+#define MK_FLAG_HISTORY_FULL      0x100u /* mk_decode_commit: the row's history buffer is full, the token was not appended;
+                                           sampling: history_len[b] exceeded min(history_ld, 65535) and was clamped to it */
 
 /* Field for field mako::gen::SamplingParams (src/gen/sampler.hpp:12-20). temperature <= 0 selects greedy. */
 typedef struct mk_sampling_params {
@@ -70,7 +71,8 @@ typedef struct mk_rows {
     uint32_t n_history;          /* history entries per row when history_len == NULL; <= 65535 */
     const int32_t* history;      /* device [batch][history_ld] generated-token ids = accept() calls (sampler.cpp:15-18) */
     uint64_t history_ld;
-    const int32_t* history_len;  /* device [batch] or NULL */
+    const int32_t* history_len;  /* device [batch] or NULL; a value above min(history_ld, 65535) is clamped to it
+                                    and reported as MK_FLAG_HISTORY_FULL */
     const uint32_t* mask;        /* device [batch][mask_ld]; bit id%32 of word id/32 set = allowed; NULL = all */
     uint64_t mask_ld;
     const mk_bias* bias;         /* device [batch][n_bias] or NULL */
@@ -188,7 +190,8 @@ int mk_rank_force(mk_sampler* s, const float* logits, uint64_t ld, uint32_t batc
  * history[b][history_len[b]++] — what Sampler::accept does (sampler.cpp:15-18); the next sample call reads the same
  * buffers through mk_rows.history / history_len. A row whose history is full keeps its length and gets
  * MK_FLAG_HISTORY_FULL or-ed into flags[b] (optional); a sampled token < 0 (a failed row) is not committed.
- * All pointers are device pointers. */
+ * history_cap is at most 65535 (the sampler counts a token's occurrences in 16 bits). All pointers are device
+ * pointers. */
 int mk_decode_commit(mk_sampler* s, uint32_t batch, const int32_t* sampled, const int32_t* forced, int32_t* history,
                      uint64_t history_ld, uint32_t history_cap, int32_t* history_len, int32_t* next_input,
                      int32_t* committed, uint32_t* flags, void* stream);
@@ -199,6 +202,8 @@ int mk_decode_commit(mk_sampler* s, uint32_t batch, const int32_t* sampled, cons
  * e.g. ncclAllGather) and calls mk_sampler_vp_merge on every rank (or one). */
 uint32_t mk_vp_record_bytes(uint32_t k);
 int mk_sampler_vp_local(mk_sampler* s, const mk_rows* shard_rows, uint32_t k, void* records, void* stream);
+/* Shard g of the gathered records must hold columns that all lie below shard g+1's (any widths, equal or not);
+ * n_vocab_total <= 2^26. */
 int mk_sampler_vp_merge(mk_sampler* s, const void* gathered, uint32_t n_shards, uint32_t batch, uint32_t k,
                         uint32_t n_vocab_total, const mk_sampling_params* params, const float* u,
                         const mk_sample_out* out, void* stream);
@@ -211,7 +216,11 @@ int mk_sampler_sample_host(mk_sampler* s, const mk_rows* host_rows, const float*
 /* The reference's own object, one row at a time with its own state: replaces mako::gen::Sampler
  * (src/gen/sampler.hpp:22-45) call for call. Keeps the parameters, the generated-token history (accept,
  * sampler.cpp:15-18) and a std::mt19937_64 seeded like the reference's, from which it takes the same uniforms in
- * the same order: one per sample(), one per verify() plus one more after a rejection, none when greedy. `logits`
+ * the same order: one per sample(), one per verify() plus one more after a rejection, none when greedy. With the
+ * same seed the token stream is the reference's, with one exception: top_k active and top_p >= 1. There the reference
+ * walks its candidates in the order std::nth_element happened to leave them (sampler.cpp:41, 64-73), which no
+ * specification fixes; this library walks them sorted by (weight descending, id ascending). The candidate set and
+ * every probability are the same, the draw order is not, so the streams differ in that one case. `logits`
  * may be a host pointer (copied, as the reference's callers hold host rows) or a device pointer (read in place).
  * include/mako_b200/sampler.hpp wraps these five calls in a C++ class with the reference's signatures. */
 typedef struct mk_row_sampler mk_row_sampler;

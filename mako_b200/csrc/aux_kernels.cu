@@ -13,6 +13,7 @@ namespace {
 
 constexpr int kMergeThreads = 128;
 constexpr int kMergeCap = 2048; // n_shards * k
+constexpr uint32_t kShardShift = 26, kIdMask = (1u << kShardShift) - 1u; // sort keys: shard above the token id
 
 __device__ void sort_keys(unsigned long long* keys, uint32_t n2, uint32_t n_threads)
 {
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
 
     // global maximum and first argmax
     float m = ninf;
-    uint32_t arg_id = 0;
+    uint32_t arg_id = 0, arg_shard = 0;
     bool any = false, nan0 = false;
     for (uint32_t g = 0; g < a.n_shards; ++g) {
         const float mg = *reinterpret_cast<const float*>(rec(g));
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
             if (!any || mg > m) { // shards ascend in id, so the first shard holding the maximum wins ties
                 m = mg;
                 arg_id = first.y;
+                arg_shard = g;
                 any = true;
             }
         }
@@ -79,6 +81,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
     if (nan0) {
         m = __int_as_float(0x7fc00000);
         arg_id = 0;
+        arg_shard = 0;
     }
     if (tid == 0) {
         s_n = 0;
@@ -101,7 +104,9 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
         return;
     }
 
-    // exact weights; key carries the shard in the low bits of a side table (recomputed from id ranges later)
+    // exact weights. The id field of a key carries the shard the candidate came from in its top six bits (ids stay
+    // below 2^26, checked by the caller): shards ascend in id, so the order by id is unchanged, and the count of a
+    // shard's members in the deciding set below needs no knowledge of how the columns were split.
     if (!nan0) {
         for (uint32_t e = tid; e < a.n_shards * a.k; e += kMergeThreads) {
             const uint32_t g = e / a.k, i = e % a.k;
@@ -113,7 +118,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
             const float q = expf_host_exact(x);
             if (q >= minp_eff && q > 0.0f) {
                 const uint32_t slot = atomicAdd(&s_n, 1u);
-                keys[slot] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
+                keys[slot] = ((unsigned long long)__float_as_uint(q) << 32) | (g << kShardShift) | c.y;
             }
         }
     }
@@ -122,7 +127,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
     if (n == 0) {
         flags |= MK_FLAG_NO_CANDIDATE;
         if (tid == 0)
-            keys[0] = ((unsigned long long)__float_as_uint(1.0f) << 32) | arg_id;
+            keys[0] = ((unsigned long long)__float_as_uint(1.0f) << 32) | arg_shard << kShardShift | arg_id;
         n = 1;
         __syncthreads();
     }
@@ -152,10 +157,11 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
             const unsigned long long key = keys[i];
             return sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
         };
-        auto id_at = [&](uint32_t i) -> uint32_t {
+        auto tag_at = [&](uint32_t i) -> uint32_t { // shard << kShardShift | token id
             const unsigned long long key = keys[i];
             return sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
         };
+        auto id_at = [&](uint32_t i) -> uint32_t { return tag_at(i) & kIdMask; };
         // A shard whose whole list is inside the deciding set may hold further members the merge cannot see.
         uint32_t n_decide = n; // the set whose completeness matters: all candidates when the total is their sum
         if (cut_k)
@@ -196,12 +202,8 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
         else if (cut_k)
             n_decide = min(n_decide, prm.top_k);
         // count members per shard among the deciding set
-        const uint32_t shard_w = (a.n_vocab_total + a.n_shards - 1) / a.n_shards;
-        for (uint32_t i = 0; i < n_decide; ++i) {
-            const uint32_t g = min(id_at(i) / max(shard_w, 1u), a.n_shards - 1);
-            if (g < 64)
-                s_shard_in[g] += 1;
-        }
+        for (uint32_t i = 0; i < n_decide; ++i)
+            s_shard_in[tag_at(i) >> kShardShift] += 1;
         for (uint32_t g = 0; g < a.n_shards && g < 64; ++g) {
             const uint32_t hdr = *reinterpret_cast<const uint32_t*>(rec(g) + 4);
             const uint32_t ng = hdr & 0xffffu;
@@ -238,7 +240,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
         const uint32_t nf = min(s_nfinal, a.cand_cap);
         for (uint32_t i = tid; i < nf; i += kMergeThreads) {
             const unsigned long long key = keys[i];
-            const uint32_t id = sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
+            const uint32_t id = (sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32)) & kIdMask;
             const float q = sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
             if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)id;
             if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + i] = q;
@@ -406,12 +408,17 @@ cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream)
     while (cap2 < a.cap)
         cap2 <<= 1;
     const size_t smem = 2 * (size_t)cap2 * 8;
-    static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(pq_resolve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static bool configured[64] = {}; // the attribute is per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return e;
+    if (smem > 48 * 1024 && !(dev >= 0 && dev < 64 && configured[dev])) {
+        e = cudaFuncSetAttribute(pq_resolve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess)
             return e;
-        configured = true;
+        if (dev >= 0 && dev < 64)
+            configured[dev] = true;
     }
     pq_resolve_kernel<<<a.batch, kPqThreads, smem, stream>>>(a);
     return cudaGetLastError();

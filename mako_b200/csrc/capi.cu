@@ -461,6 +461,9 @@ int mk_decode_commit(mk_sampler* s, uint32_t batch, const int32_t* sampled, cons
     if (history_ld < history_cap)
         return fail(MK_ERR_INVALID_ARGUMENT, "mk_decode_commit: history_ld %llu below history_cap %u",
                     (unsigned long long)history_ld, history_cap);
+    if (history_cap > 65535u)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_decode_commit: history_cap %u above 65535 (the sampler counts a "
+                                             "token's occurrences in 16 bits)", history_cap);
     DeviceGuard g(s->device);
     MK_CUDA(mk::launch_decode_commit(batch, sampled, forced, history, history_ld, history_cap, history_len, next_input,
                                      committed, flags, (cudaStream_t)stream));
@@ -508,6 +511,9 @@ int mk_sampler_vp_merge(mk_sampler* s, const void* gathered, uint32_t n_shards, 
         return fail(MK_ERR_INVALID_ARGUMENT, "n_shards in 1..64, k in 1..%u, n_shards*k <= 2048", mk::kVpMaxK);
     if (!u && params->temperature > 0.0f)
         return fail(MK_ERR_INVALID_ARGUMENT, "uniforms are required unless greedy");
+    if (n_vocab_total > (1u << 26))
+        return fail(MK_ERR_INVALID_ARGUMENT, "n_vocab_total %u above 2^26 (the merge keeps the shard beside the id)",
+                    n_vocab_total);
     DeviceGuard g(s->device);
     mk::VpMergeArgs a;
     std::memset(&a, 0, sizeof a);
@@ -535,6 +541,13 @@ int mk_sampler_sample_host(mk_sampler* s, const mk_rows* hr, const float* u, con
         return fail(MK_ERR_INVALID_ARGUMENT, "mk_sampler_sample_host: null argument");
     if (hr->params_dev)
         return fail(MK_ERR_INVALID_ARGUMENT, "host form takes shared params only");
+    if (hr->history_len)
+        return fail(MK_ERR_INVALID_ARGUMENT, "host form takes one history length for all rows (n_history); "
+                                             "history_len must be NULL");
+    if (int rc = check_rows(s, hr)) // strides, sizes and limits, before any of them sizes the staging buffer
+        return rc;
+    if (!u && !all_greedy(hr))
+        return fail(MK_ERR_INVALID_ARGUMENT, "uniforms are required unless every row is greedy");
     DeviceGuard g(s->device);
     const size_t B = hr->batch, V = hr->n_vocab;
     const size_t ldd = (V + 3) & ~size_t(3);

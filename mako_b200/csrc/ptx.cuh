@@ -85,12 +85,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
 // so that a batch of rows larger than L2 does not push out what is used again (code, histories, scratch).
 __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar)
 {
-#ifdef MK_NO_L2_HINT
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst_smem)),
-                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-#else
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     asm volatile(
@@ -98,7 +92,6 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
             smem_u32(dst_smem)),
         "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
-#endif
 }
 
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t n_threads)

@@ -39,18 +39,11 @@
 #include <cfloat>
 #include <type_traits>
 
-#ifndef MK_TILE
-#define MK_TILE 4096
-#endif
-#ifndef MK_STAGES
-#define MK_STAGES 4
-#endif
-
 namespace mk {
 
 namespace {
 
-constexpr int kTile = MK_TILE;   // floats per tile
+constexpr int kTile = 4096;     // floats per tile
 constexpr int kMaxStages = 7;  // ring stages that fit when a row needs no tables
 constexpr int kProducerThreads = 32;
 constexpr int kFixers = 64;
@@ -61,20 +54,13 @@ constexpr int kVec = kTile / (kReaders * 4); // 128-bit loads per reader thread 
 constexpr int kEl = kVec * 4;
 static_assert(kVec * kReaders * 4 == kTile, "a tile is a whole number of 128-bit loads per reader thread");
 constexpr int kHistCap = 4096;  // history entries de-duplicated in shared memory; longer histories scan global memory
-#ifndef MK_BM_WORDS
-#define MK_BM_WORDS 5120
-#endif
-constexpr int kBmWords = MK_BM_WORDS;  // history bitmap: one bit per column, vocabularies up to 163840 columns
+constexpr int kBmWords = 5120;  // history bitmap: one bit per column, vocabularies up to 163840 columns
 constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
 constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) once the streaming is over
-#ifndef MK_BINS
-#define MK_BINS 2048
-#define MK_BINSHIFT 21
-#endif
 constexpr uint32_t kBarSort = 3;         // named barrier of the sorting warps
 constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates kept
-constexpr int kBins = MK_BINS;     // top_k histogram: 11 leading bits of the order key
-constexpr int kBinShift = MK_BINSHIFT;
+constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
+constexpr int kBinShift = 21;
 
 // Shared memory of a CTA: this fixed head, then kDynBytes laid out per row. While the row streams: the tables the
 // row needs (generated-column bitmap, per-word ranks, counts; the top_k histogram) and, in all that is left, the
@@ -754,7 +740,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
     // Whether the history matters is known from three comparisons; its loads (the first thing the set-up waits for)
     // are issued before the rest of the parameters is worked out.
-    const uint32_t hlen_all = a.history ? (a.history_len ? (uint32_t)max(a.history_len[row], 0) : a.n_history) : 0u;
+    // A per-row length read from device memory is clamped to what the row's buffer holds and to the 16-bit counters
+    // of the long-history path; a clamp that bites is reported in the row's flags (MK_FLAG_HISTORY_FULL).
+    const uint32_t hlen_cap = (uint32_t)min((uint64_t)65535u, a.history_ld);
+    const uint32_t hlen_dev = (a.history && a.history_len) ? (uint32_t)max(a.history_len[row], 0) : 0u;
+    const bool hlen_clamped = hlen_dev > hlen_cap;
+    const uint32_t hlen_all = a.history ? (a.history_len ? min(hlen_dev, hlen_cap) : a.n_history) : 0u;
     const bool has_hist = !(prm.temperature <= 0.0f) && hlen_all > 0 &&
                           !(prm.repetition_penalty == 1.0f && prm.presence_penalty == 0.0f && prm.frequency_penalty == 0.0f);
     const uint32_t hlen = has_hist ? hlen_all : 0u;
@@ -983,9 +974,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 break;
             if (a.use_bulk_copy) {
                 if (lane == 0) {
-#ifndef MK_NO_FENCE
                     fence_proxy_async();
-#endif
                     const uint32_t bytes = (n_t * 4u) & ~15u;
                     for (uint32_t e = bytes / 4; e < n_t; ++e)
                         dst[e] = src[e];
@@ -1278,7 +1267,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         m = __int_as_float(0x7fc00000);
         arg_col = 0;
     }
-    uint32_t flags = 0;
+    uint32_t flags = hlen_clamped ? MK_FLAG_HISTORY_FULL : 0u;
     if (mrow && !any_finite && !s.nan0)
         flags |= MK_FLAG_ALL_MASKED;
 
@@ -1547,11 +1536,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 
     if (cut_k) {
         // sampler.cpp:40-42. Ties in q with the k-th weight are ordered by id among ALL elements with that weight;
-        // elements below the histogram bound were not collected, so the bound itself must map to a strictly
-        // smaller weight than the k-th.
+        // elements below the histogram bound were not collected, so the largest value below the bound must map to a
+        // strictly smaller weight than the k-th (weights are monotone in the logit).
         const float qk = q_of(cfg.top_k - 1);
-        const float edge = key_to_float(s.thr_topk_key);
-        if (edge > -FLT_MAX && expf_host_exact(__fmul_rn(__fsub_rn(edge, m), cfg.inv_t)) >= qk)
+        const uint32_t edge_key = s.thr_topk_key;
+        const float below = key_to_float(edge_key - 1u);
+        if (edge_key > order_key(-FLT_MAX) && expf_host_exact(__fmul_rn(__fsub_rn(below, m), cfg.inv_t)) >= qk)
             flags |= MK_FLAG_GUARD_BAND;
         n = cfg.top_k;
     }

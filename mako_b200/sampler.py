@@ -15,24 +15,8 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import RowsC, SampleOutC, SamplingParamsC, check, lib
-
-
-@dataclass
-class SamplingParams:
-    """Applied in this order: penalties, temperature, min_p, top_k, top_p (src/gen/sampler.hpp:11-20)."""
-
-    temperature: float = 1.0
-    top_k: int = 0
-    top_p: float = 1.0
-    min_p: float = 0.0
-    presence_penalty: float = 0.0
-    frequency_penalty: float = 0.0
-    repetition_penalty: float = 1.0
-
-    def to_c(self) -> SamplingParamsC:
-        return SamplingParamsC(self.temperature, self.top_k, self.top_p, self.min_p, self.presence_penalty,
-                               self.frequency_penalty, self.repetition_penalty)
+from ._lib import RowsC, SampleOutC, check, lib
+from .params import SamplingParams
 
 
 def check_sampling(p: SamplingParams) -> None:

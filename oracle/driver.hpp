@@ -294,16 +294,22 @@ template <class Engine> struct Driver {
                 tokens[b] = c[walk(c, u[b] * total)].second;
             }
         };
+        auto pass = [&]() {
+            if (n_threads == 1) {
+                work(0);
+            } else {
+                std::vector<std::thread> pool;
+                for (uint32_t t = 0; t < n_threads; ++t)
+                    pool.emplace_back(work, t);
+                for (auto& th : pool)
+                    th.join();
+            }
+        };
+        // One untimed pass first: a sampler's work and candidate vectors are allocated by its first call, which a
+        // long-lived reference Sampler pays once per request, not once per token. The timed pass is the steady state.
+        pass();
         const auto t0 = std::chrono::steady_clock::now();
-        if (n_threads == 1) {
-            work(0);
-        } else {
-            std::vector<std::thread> pool;
-            for (uint32_t t = 0; t < n_threads; ++t)
-                pool.emplace_back(work, t);
-            for (auto& th : pool)
-                th.join();
-        }
+        pass();
         return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     }
 };

@@ -77,8 +77,9 @@ int orc_sample_rng(const orc_params* p, const orc_row* row, uint64_t seed, uint3
  * each: what the reference multiplies `total` with (sampler.cpp:66). */
 void orc_uniforms(uint64_t seed, uint32_t n, float* out);
 
-/* Times sample() over a batch of rows spread over n_threads host threads; sampler construction and the history
- * replay are outside the timed region, bias/mask pre-processing is inside. Rows share params; row b reads
+/* Times sample() over a batch of rows spread over n_threads host threads; sampler construction, the history
+ * replay and one untimed pass over the batch (which sizes each sampler's work vectors, as the first token of a
+ * request does) are outside the timed region, bias/mask pre-processing is inside. Rows share params; row b reads
  * logits + b*ld, history + b*n_history, mask + b*mask_ld, bias + b*n_bias, u[b]. Returns seconds, <0 on error. */
 double orc_time_sample_batch(const orc_params* p, uint32_t batch, uint32_t n_vocab, const float* logits, uint64_t ld,
                              const int32_t* history, uint32_t n_history, const uint32_t* mask, uint64_t mask_ld,

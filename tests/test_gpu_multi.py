@@ -9,6 +9,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 V, B, H, K = 151552, 16, 4096, 64
+P_TOPP_KW = dict(temperature=0.8, top_p=0.9, repetition_penalty=1.1, presence_penalty=0.5, frequency_penalty=0.3)
 
 
 def _worker(rank, world, port, q):
@@ -17,6 +18,7 @@ def _worker(rank, world, port, q):
     import torch.distributed as dist
     from mako_b200 import BatchSampler, SamplingParams, synth
     from mako_b200.parallel import row_shard, vocab_parallel_sample, vocab_shard
+    P_TOPP = SamplingParams(**P_TOPP_KW)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -27,15 +29,23 @@ def _worker(rank, world, port, q):
         u = synth.uniforms(333, B)
         s = BatchSampler(V, B, rank, cand_cap=0)
         lo, hi = vocab_shard(V, rank, world)
-        res = vocab_parallel_sample(s, torch.from_numpy(np.ascontiguousarray(logits[:, lo:hi])).cuda(), p,
-                                    torch.from_numpy(u).cuda(), V, K, history=torch.from_numpy(hist).cuda())
+        shard = torch.from_numpy(np.ascontiguousarray(logits[:, lo:hi])).cuda()
+        d_u, d_hist = torch.from_numpy(u).cuda(), torch.from_numpy(hist).cuda()
+        res = vocab_parallel_sample(s, shard, p, d_u, V, K, history=d_hist, exact=False)
         torch.cuda.synchronize()
         vp_tok, vp_flags = res.token.cpu().numpy().copy(), res.flags.cpu().numpy().copy()
+        # top_p alone: flat rows have nuclei longer than a shard's list; the second round makes them exact
+        res = vocab_parallel_sample(s, shard, P_TOPP, d_u, V, K, history=d_hist, exact=False)
+        torch.cuda.synchronize()
+        n_trunc = int((res.flags.cpu().numpy() & 0x20 != 0).sum())
+        res = vocab_parallel_sample(s, shard, P_TOPP, d_u, V, K, history=d_hist, exact=True)
+        torch.cuda.synchronize()
+        ex_tok, ex_flags = res.token.cpu().numpy().copy(), res.flags.cpu().numpy().copy()
         rlo, rhi = row_shard(B, rank, world)
         res = s.sample(torch.from_numpy(logits[rlo:rhi]).cuda(), p, torch.from_numpy(u[rlo:rhi]).cuda(),
                        history=torch.from_numpy(hist[rlo:rhi]).cuda())
         torch.cuda.synchronize()
-        q.put((rank, vp_tok, vp_flags, rlo, res.token.cpu().numpy().copy()))
+        q.put((rank, vp_tok, vp_flags, rlo, res.token.cpu().numpy().copy(), n_trunc, ex_tok, ex_flags))
     finally:
         dist.destroy_process_group()
 
@@ -64,5 +74,14 @@ def test_two_gpu_vocab_parallel_and_row_sharded(ref):
     assert np.array_equal(out[0][1], out[1][1])            # every rank merges to the same tokens
     exact = [i for i in range(B) if not (out[0][2][i] & 0x22)]
     assert len(exact) >= B - 2 and all(out[0][1][i] == want[i] for i in exact)
-    for rank, _, _, rlo, toks in out:                      # row-sharded: always exact
+    for rank, _, _, rlo, toks, *_ in out:                  # row-sharded: always exact
         assert np.array_equal(toks, want[rlo:rlo + len(toks)])
+    # top_p alone with the second round: every row not in a numeric guard band returns the reference's token, and no
+    # row is left reported as truncated
+    p2 = SamplingParams(**P_TOPP_KW)
+    want2 = np.array([ref.sample(p2, logits[i], u[i], history=hist[i])["token"] for i in range(B)])
+    assert np.array_equal(out[0][6], out[1][6])
+    assert not (out[0][7] & 0x20).any()
+    sure = [i for i in range(B) if not (out[0][7][i] & 0x2)]
+    assert len(sure) >= B - 2 and all(out[0][6][i] == want2[i] for i in sure)
+    print(f"two-GPU vocab-parallel: {out[0][5]} of {B} top_p-alone rows took the second round")

@@ -6,7 +6,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mako_b200.parallel import gather_records, row_shard, shard_width, vocab_shard
+from mako_b200.parallel import gather_columns, gather_records, row_shard, shard_width, shard_widths, vocab_shard
 
 
 def test_row_shards_partition_the_batch():
@@ -29,6 +29,18 @@ def test_vocab_shards_are_word_aligned_and_cover_the_vocabulary():
         vocab_shard(100, 2, 2)
 
 
+def test_uneven_vocab_shards():
+    # 151936 columns are 4748 words: 8 ranks get 594 or 593 words each, the wider ones first
+    spans = [vocab_shard(151936, r, 8) for r in range(8)]
+    assert [hi - lo for lo, hi in spans] == [19008] * 4 + [18976] * 4
+    assert shard_widths(151936, 8) == [19008] * 4 + [18976] * 4
+    assert shard_widths(151936, 8, 32) == [594] * 4 + [593] * 4
+    assert shard_width(151936, 8) == 19008
+    # a vocabulary that ends inside a word: the last shard is the ragged one, its mask still a whole word
+    assert shard_widths(1000, 3) == [352, 352, 296] and shard_widths(1000, 3, 32) == [11, 11, 10]
+    assert sum(shard_widths(129280, 3)) == 129280
+
+
 def _worker(rank, world, port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -44,7 +56,13 @@ def _worker(rank, world, port, q):
         lo, hi = row_shard(10, rank, world)
         t = torch.tensor([hi - lo])
         dist.all_reduce(t)
-        q.put((rank, ok and int(t.item()) == 10))
+        ok = ok and int(t.item()) == 10
+        # whole rows from uneven column shards (1000 columns over two ranks: 512 + 488)
+        full = torch.arange(3 * 1000, dtype=torch.float32).reshape(3, 1000)
+        clo, chi = vocab_shard(1000, rank, world)
+        rows = gather_columns(full[:, clo:chi].contiguous(), shard_widths(1000, world))
+        ok = ok and bool(torch.equal(rows, full))
+        q.put((rank, ok))
     finally:
         dist.destroy_process_group()
 

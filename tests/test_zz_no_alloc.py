@@ -3,9 +3,12 @@
 Some users of this library cannot call cudaMalloc where they sample: their process hands out all device memory at
 start-up, or they are a plugin inside a runtime whose allocator they must not touch, so they cannot create a sampler
 handle (its scratch is allocated). For them the library keeps a fixed scratch array of its own. This test calls that
-entry point through the C ABI twice in a row (the array keeps the previous call's contents) and expects the very
-same tokens, probabilities, candidate counts and flags as the ordinary entry point. It is collected last so that a
-run that stops at the first failure has already run everything else; it passes alone as well as after the others."""
+entry point through the C ABI several times in a row (the array keeps the previous call's contents) and expects the
+very same tokens, probabilities, candidate counts and flags as the ordinary entry point, and the tokens of the CPU
+reference. One of the cases is top_p alone, where the kernel is launched a second time for the rows that marked
+themselves in the scratch array: the mark sits behind the candidate area, whose size differs between the library's
+array and a handle's buffer. It is collected last so that a run that stops at the first failure has already run
+everything else; it passes alone as well as after the others."""
 import ctypes as C
 
 import numpy as np
@@ -27,7 +30,7 @@ def _call_static(lib, rows_c, u, out_tensors, cand_cap=0):
     assert rc == 0, lib.mk_last_error().decode()
 
 
-def test_static_scratch_entry_point_matches_handle_entry_point():
+def test_static_scratch_entry_point_matches_handle_entry_point(ref):
     import torch
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
@@ -38,8 +41,12 @@ def test_static_scratch_entry_point_matches_handle_entry_point():
         SamplingParams(temperature=0.8, top_p=0.9, min_p=0.05, repetition_penalty=1.1, presence_penalty=0.5,
                        frequency_penalty=0.3),
         SamplingParams(temperature=0.7, top_k=40, top_p=0.95),
+        # top_p alone: rows that the first launch cannot settle are streamed again by a second launch
+        SamplingParams(temperature=0.6, top_p=0.95),
+        SamplingParams(temperature=0.8, top_p=0.9, repetition_penalty=1.1, presence_penalty=0.5, frequency_penalty=0.3),
     ]
-    for call, params in enumerate(cases):          # two calls in a row share the library's scratch array
+    second_pass_rows = 0
+    for call, params in enumerate(cases):          # calls in a row share the library's scratch array
         logits, _ = synth.logits(900 + call, b, v)
         hist = synth.history_zipf(900 + call, b, v, h)
         u = synth.uniforms(900 + call, b)
@@ -60,6 +67,17 @@ def test_static_scratch_entry_point_matches_handle_entry_point():
         for k in want:
             a = got[k].cpu().numpy()
             assert np.array_equal(a.view(np.uint32), want[k].view(np.uint32)), f"call {call}: {k} differs"
+        # and against the CPU reference, row by row
+        tok, flags, ncand = (got[k].cpu().numpy() for k in ("token", "flags", "n_cand"))
+        assert not (flags & 0x50).any()
+        for i in range(b):
+            w = ref.sample(params, logits[i], u[i], history=hist[i])
+            if flags[i] & 0x2:
+                continue
+            assert tok[i] == w["token"] and ncand[i] == w["n_cand"], f"call {call} row {i}"
+        if params.min_p == 0 and params.top_k == 0:
+            second_pass_rows += int((ncand > 256).sum())   # a nucleus beyond the first launch's 256 kept elements
+    assert second_pass_rows > 0, "no row of the top_p-alone cases took the second launch"
 
 
 def test_static_entry_point_rejects_sizes_beyond_its_limits():
