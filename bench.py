@@ -436,8 +436,11 @@ def config4_block(timer: Timer, dev, rank: int, world: int, local_rank: int, pea
         blk.update(rows_compared=int(sure.sum()),
                    token_mismatches_vs_cpu=int((vp_tok[sure] != want_cpu[sure]).sum()))
     # the second round for rows whose nucleus reaches past a shard's list: whole rows gathered, single-device kernel
+    res = vocab_parallel_sample(vp, shard_of(0), params, u, v, VP_K, history=hist, exact=True)  # untimed warm-up
+    torch.cuda.synchronize(dev)
+    timer.barrier()
     t0 = time.perf_counter()
-    reps = 3
+    reps = 5
     for _ in range(reps):
         res = vocab_parallel_sample(vp, shard_of(0), params, u, v, VP_K, history=hist, exact=True)
         torch.cuda.synchronize(dev)
@@ -576,6 +579,9 @@ def main() -> None:
     ap.add_argument("--no-config4", action="store_true", help="skip the scale-out block of the JSON line")
     ap.add_argument("--streams", type=int, default=2, help="batches in flight (sampler handles and streams)")
     ap.add_argument("--no-graph", action="store_true", help="launch each step from the host instead of a CUDA graph")
+    ap.add_argument("--overlap", type=int, default=2, choices=[0, 1, 2],
+                    help="how a launch follows the previous kernel of its stream: 0 plain stream order, 1 programmatic "
+                         "dependent launch, 2 the same with the history tables built before the wait")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -616,6 +622,8 @@ def main() -> None:
     # batches in flight, as a server that double-buffers its decode steps has them, so that one launch's set-up and
     # finish overlap the other's streaming instead of leaving the memory system idle.
     samplers = [BatchSampler(v, b, local_rank) for _ in range(max(1, args.streams))]
+    for smp in samplers:
+        smp.set_overlap(args.overlap)
     sampler = samplers[0]
 
     def step(k, handle=None):
@@ -685,7 +693,10 @@ def main() -> None:
         conf.update(l2=f"{N_SETS} distinct input sets cycled ({N_SETS * rb * b / 1e6:.0f} MB > L2)",
                     launch="host loop" if args.no_graph else
                     f"CUDA graph of {PER_GRAPH} steps replayed {t['replays']} times, one event pair per replay, "
-                    f"{len(samplers)} batches in flight")
+                    f"{len(samplers)} batches in flight",
+                    overlap=["plain stream order", "programmatic dependent launch",
+                             "programmatic dependent launch, history tables built before the wait (histories and "
+                             "parameters are not written by the previous kernel)"][args.overlap])
         line = {
             "metric": "sampled rows/s", "value": world * b / (ms_step / 1e3), "unit": "rows/s", "n_gpus": world,
             "steps": t["steps"], "warmup": args.warmup, "ms_per_step": ms_step, "ms_per_step_p10": t["p10"],

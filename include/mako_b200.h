@@ -109,6 +109,23 @@ void mk_sampler_destroy(mk_sampler* s);
  * temperature 0 or >= 1e-3, repetition_penalty in (0, 100], |presence|, |frequency| <= 100. */
 int mk_check_sampling(const mk_sampling_params* p);
 
+/* No counterpart in the reference (its sampler runs on the host, between two engine steps). How the row kernel of
+ * this handle's sample / verify calls is launched behind the kernel that precedes it in the stream:
+ *   MK_OVERLAP_OFF                 plain stream order (the default);
+ *   MK_OVERLAP_LAUNCH              programmatic dependent launch: the kernel's CTAs may be scheduled while the
+ *                                  previous kernel drains, and wait for its completion before they touch any memory.
+ *                                  Always safe; hides the launch gap;
+ *   MK_OVERLAP_STABLE_SIDE_INPUTS  the same, and the caller promises that the previous kernel in the stream writes
+ *                                  none of params_dev, history, history_len and bias of the call: the kernel then
+ *                                  builds its per-row history tables before it waits, so that only streaming the
+ *                                  logits is left once the previous kernel (the one that produces the logits, or the
+ *                                  previous sample call) has finished. Logits, mask, uniforms and drafts are read,
+ *                                  and everything is written, after the wait. */
+#define MK_OVERLAP_OFF 0
+#define MK_OVERLAP_LAUNCH 1
+#define MK_OVERLAP_STABLE_SIDE_INPUTS 2
+int mk_sampler_set_overlap(mk_sampler* s, int mode);
+
 /* Replaces Sampler::sample (sampler.cpp:75-84) for rows->batch rows: u[b] in [0,1) is the uniform the reference
  * would draw from its generator (r = u * total, sampler.cpp:66). One kernel, one pass over the logits. */
 int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, const mk_sample_out* out,

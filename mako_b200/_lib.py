@@ -26,6 +26,8 @@ FLAG_VP_TRUNCATED = 0x020
 FLAG_TIMEOUT = 0x040
 FLAG_HISTORY_FULL = 0x100
 
+OVERLAP_OFF, OVERLAP_LAUNCH, OVERLAP_STABLE_SIDE_INPUTS = 0, 1, 2
+
 
 class SamplingParamsC(C.Structure):
     _fields_ = [
@@ -123,6 +125,7 @@ def _load() -> C.CDLL:
     lib.mk_row_sampler_verify.argtypes = [vp, vp, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.mk_debug_expf.argtypes = [vp, vp, C.c_uint64, vp]
     lib.mk_debug_set_timing.argtypes = [vp, vp]
+    lib.mk_sampler_set_overlap.argtypes = [vp, C.c_int]
     return lib
 
 

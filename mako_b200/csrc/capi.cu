@@ -56,6 +56,7 @@ struct mk_sampler {
     int32_t* p_tok = nullptr;
     // host-buffer staging (sized on first use)
     cudaStream_t own_stream = nullptr;
+    int overlap = MK_OVERLAP_OFF;         // how the row kernel is launched behind its predecessor in the stream
     unsigned long long* timing = nullptr; // debug: per-row phase timestamps of the next launches
     unsigned long long* pick_best = nullptr; // mk_draft_pick: one packed (score, id) maximum per sequence
     unsigned char* stage = nullptr;
@@ -130,6 +131,7 @@ void fill_common(mk::RowKernelArgs& a, const mk_sampler* s, const mk_rows* r)
     a.scratch = s->scratch;
     a.scratch_cap = scratch_cap(s->n_vocab);
     a.timing = s->timing;
+    a.overlap = s->overlap;
     a.use_bulk_copy = ((reinterpret_cast<uintptr_t>(r->logits) & 15u) == 0 && (r->ld % 4u) == 0) ? 1 : 0;
 }
 
@@ -615,6 +617,16 @@ int mk_sampler_sample_host(mk_sampler* s, const mk_rows* hr, const float* u, con
     return MK_OK;
 }
 
+
+int mk_sampler_set_overlap(mk_sampler* s, int mode)
+{
+    if (!s)
+        return fail(MK_ERR_INVALID_ARGUMENT, "null sampler handle");
+    if (mode != MK_OVERLAP_OFF && mode != MK_OVERLAP_LAUNCH && mode != MK_OVERLAP_STABLE_SIDE_INPUTS)
+        return fail(MK_ERR_INVALID_ARGUMENT, "overlap mode %d is none of MK_OVERLAP_*", mode);
+    s->overlap = mode;
+    return MK_OK;
+}
 
 int mk_debug_set_timing(mk_sampler* s, unsigned long long* timing_dev)
 {

@@ -94,6 +94,19 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
         : "memory");
 }
 
+// Programmatic dependent launch. wait: blocks until the grids this one was launched behind have completed and their
+// writes are visible (returns at once in a launch without that dependency). launch_dependents: the grid launched
+// behind this one may start being scheduled once every CTA of this grid has said so or exited.
+__device__ __forceinline__ void griddep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void griddep_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t n_threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");

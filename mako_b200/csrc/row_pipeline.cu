@@ -59,6 +59,7 @@ constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
 constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) once the streaming is over
 constexpr uint32_t kBarSort = 3;         // named barrier of the sorting warps
 constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates kept
+constexpr uint32_t kNoBias = 0x7fa00001u; // a NaN payload no caller's bias carries: this rank has no bias
 constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = 21;
 
@@ -79,7 +80,7 @@ struct __align__(128) Smem {
     uint32_t hi_group;              // highest non-empty group of 32 histogram bins
     uint32_t n_final;
     uint32_t flags;
-    uint32_t n_distinct;            // distinct generated columns
+    uint32_t n_distinct;            // distinct special columns (generated or biased)
 };
 constexpr uint32_t kSmemBytes = 115712; // two CTAs per SM: (228 KB - 2 x 1 KB reserved) / 2
 constexpr uint32_t kHeadBytes = (sizeof(Smem) + 127u) & ~127u;
@@ -206,55 +207,15 @@ __device__ __forceinline__ unsigned long long pack_by_column(float q, uint32_t c
     return ((unsigned long long)col << 32) | __float_as_uint(q);
 }
 
-// Position of the n-th set bit (n = 0: the lowest) of a word that has more than n bits set: five halvings by
-// popcount (the library's find-n-th-set is a loop over the bits).
-__device__ __forceinline__ uint32_t nth_set_bit(uint32_t w, uint32_t n)
-{
-    uint32_t pos = 0;
-#pragma unroll
-    for (uint32_t width = 16; width > 0; width >>= 1) {
-        const uint32_t c = (uint32_t)__popc(w & ((1u << width) - 1u));
-        if (n >= c) {
-            n -= c;
-            pos += width;
-            w >>= width;
-        }
-    }
-    return pos;
-}
-
-// Penalties (sampler.cpp:23-28) for the generated columns with ranks [r_lo, r_hi) — the ones whose bitmap words lie
-// in [w_lo, w_hi) — spread evenly over n_thr threads (this one is `thr`): a rank is turned back into its column by a
-// binary search over the per-word ranks and a find-n-th-set-bit in the word, and indexes the count directly. Every
-// column is touched by exactly one thread. `tile` points at column `col0` of the row in shared memory.
-__device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t* wpre, const uint32_t* counts,
-                                         float* tile, uint32_t col0, uint32_t w_lo, uint32_t w_hi, uint32_t r_lo,
-                                         uint32_t r_hi, uint32_t thr, uint32_t n_thr, const RowCfg& cfg)
-{
-    for (uint32_t r = r_lo + thr; r < r_hi; r += n_thr) {
-        uint32_t lo = w_lo, hi = w_hi; // largest word in [lo, hi) whose rank is <= r
-        while (hi - lo > 1u) {
-            const uint32_t mid = (lo + hi) >> 1;
-            if ((uint32_t)wpre[mid] <= r)
-                lo = mid;
-            else
-                hi = mid;
-        }
-        const uint32_t bit = nth_set_bit(bitmap[lo], r - (uint32_t)wpre[lo]);
-        const uint32_t n = (counts[r >> 1] >> ((r & 1u) * 16u)) & 0xffffu;
-        const uint32_t loc = (lo << 5) + bit - col0;
-        tile[loc] = penalise(tile[loc], n, cfg);
-    }
-}
-
 // Exclusive prefix of the per-word popcounts of bitmap[0, bm_words) into wpre, total into s.n_distinct: a set
 // bit's rank among all set bits is then wpre[word] + popcount of the lower bits of its word. Whole CTA; the caller
-// synchronises before (bitmap complete) and after (wpre complete). Each thread takes a contiguous run of words.
+// synchronises before (bitmap complete) and after (wpre complete). Each thread takes a contiguous run of words; the
+// run length is odd, so that the lanes of a warp, one run apart, read 32 different banks.
 __device__ __forceinline__ void word_ranks(Smem& s, const uint32_t* bitmap, uint16_t* wpre, uint32_t bm_words)
 {
-    constexpr int kWordsPerThread = (kBmWords + kThreads - 1) / kThreads;
+    constexpr int kWordsPerThread = ((kBmWords + kThreads - 1) / kThreads) | 1;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t per = (bm_words + kThreads - 1) / kThreads;
+    const uint32_t per = ((bm_words + kThreads - 1) / kThreads) | 1u;
     const uint32_t w0 = min(tid * per, bm_words);
     uint32_t pc[kWordsPerThread]; // popcounts of this thread's words: all loads in flight together
     uint32_t mine = 0;
@@ -271,7 +232,7 @@ __device__ __forceinline__ void word_ranks(Smem& s, const uint32_t* bitmap, uint
         if ((int)lane >= o)
             inc += y;
     }
-    uint32_t* wtot = reinterpret_cast<uint32_t*>(s.warp_sum); // 16 words of scratch
+    uint32_t* wtot = reinterpret_cast<uint32_t*>(s.warp_sum); // 22 words of scratch
     if (lane == 31)
         wtot[warp] = inc;
     __syncthreads();
@@ -737,6 +698,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const uint32_t V = a.n_vocab;
     const uint32_t n_tiles = (V + kTile - 1) / kTile;
     const float* __restrict__ lrow = a.logits + (size_t)row * a.ld;
+    // Launched programmatically behind the previous kernel of the stream, this grid may start while that one still
+    // runs. Nothing that kernel may have written is touched before griddep_wait() — which comes first thing, unless
+    // the caller has declared the side inputs (parameters, histories, biases) stable: then the whole set-up runs
+    // ahead and only the logits, the mask, the uniforms and every write to global memory wait. The second pass reads
+    // a word the first pass wrote: it always waits first.
+    const bool early = a.overlap == MK_OVERLAP_STABLE_SIDE_INPUTS && a.pass == 0;
+    if (!early)
+        griddep_wait();
     const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
     // Whether the history matters is known from three comparisons; its loads (the first thing the set-up waits for)
     // are issued before the rest of the parameters is worked out.
@@ -750,12 +719,21 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                           !(prm.repetition_penalty == 1.0f && prm.presence_penalty == 0.0f && prm.frequency_penalty == 0.0f);
     const uint32_t hlen = has_hist ? hlen_all : 0u;
     const int32_t* __restrict__ hrow = a.history ? a.history + (size_t)row * a.history_ld : nullptr;
-    const bool long_history = hlen > (uint32_t)kHistCap || V > kMaxBitmapVocab;
+    const uint32_t nb = a.bias ? a.n_bias : 0u;
+    const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
+    // Columns whose value is not the one in memory — generated tokens (penalties) and biased tokens — are "special":
+    // two fix-up warps edit them in every tile in shared memory before the readers see it. While they are few (the
+    // usual case) a bitmap names them, with rank-indexed tables of counts and biases behind it, and a fix-up lane
+    // walks the set bits of its 128 columns; a longer history, or a vocabulary beyond the bitmap, takes the slower
+    // path where one warp matches the whole history against every tile.
+    const bool has_special = has_hist || nb > 0;
+    const bool use_table = has_special && hlen + nb <= (uint32_t)kHistCap && V <= kMaxBitmapVocab;
+    const bool tile_fix = has_special && !use_table;
     // The history is read into registers first thing, all loads in flight together, so that their latency
     // overlaps the barrier set-up instead of being paid once per loop trip.
     constexpr int kHistPerThread = (kHistCap + kThreads - 1) / kThreads;
     uint32_t hc[kHistPerThread]; // the entries as columns of this row (ids outside it: 0xffffffff, as past-the-end)
-    if (has_hist && !long_history) { // = use_table
+    if (use_table) {
 #pragma unroll
         for (int i = 0; i < kHistPerThread; ++i) {
             const uint32_t j = (uint32_t)i * kThreads + tid;
@@ -763,9 +741,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
     }
     const RowCfg cfg = make_cfg(prm, V, a.mode, a.vp_k, a.pass);
-    const uint32_t nb = a.bias ? a.n_bias : 0u;
-    const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
-    const bool has_fix = nb > 0 || has_hist; // work for the fix-up warps
     const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
     // Per-row scratch, 16 bytes per column: scratch_cap raw candidates (logit bits, column) — sorted in place as
     // 64-bit keys by the large sorted-list path — then as much again: the merge sort's second buffer, or (large
@@ -776,31 +751,28 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     uint32_t* const again = row_scratch + 4u * a.scratch_cap; // set by the first launch: this row wants the second pass
     if (a.pass == 1 && again[0] == 0u)
         return;
-    if (a.pass == 0 && tid == 0)
-        again[0] = 0u;
-
-    const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
-    const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
-    const int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
     // ---- shared-memory layout of the streaming phase ---------------------------------------------------------------
-    const bool use_table = has_hist && !long_history;
+    const bool use_bias = use_table && nb > 0;
     const uint32_t bm_words = (V + 31u) / 32u;
     unsigned char* const dyn = smem_raw + kHeadBytes;
     uint32_t off = 0;
-    uint32_t* const bitmap = reinterpret_cast<uint32_t*>(dyn + off); // long histories: per-tile id counters instead
-    off += use_table ? ((bm_words * 4u + 15u) & ~15u) : (long_history ? (uint32_t)kTile * 2u : 0u);
-    uint16_t* const wpre = reinterpret_cast<uint16_t*>(dyn + off);
+    uint32_t* const bitmap = reinterpret_cast<uint32_t*>(dyn + off); // tile_fix: per-tile id counters instead
+    off += use_table ? ((bm_words * 4u + 15u) & ~15u) : (tile_fix ? (uint32_t)kTile * 2u : 0u);
+    uint16_t* const wpre = reinterpret_cast<uint16_t*>(dyn + off); // rank of each bitmap word's first set bit
     off += use_table ? ((bm_words * 2u + 15u) & ~15u) : 0u;
-    uint32_t* const counts = reinterpret_cast<uint32_t*>(dyn + off);
+    uint32_t* const counts = reinterpret_cast<uint32_t*>(dyn + off); // by rank: occurrences, two per word
     off += use_table ? (uint32_t)kHistCap * 2u : 0u;
+    uint32_t* const biasval = reinterpret_cast<uint32_t*>(dyn + off); // by rank: bias as float bits, or kNoBias
+    off += use_bias ? (uint32_t)kHistCap * 4u : 0u;
     uint32_t* const hist = reinterpret_cast<uint32_t*>(dyn + off);
     off += cfg.hist_mode ? (uint32_t)kBins * 4u : 0u;
     off = (off + 127u) & ~127u;
     float* const ring = reinterpret_cast<float*>(dyn + off);
     const uint32_t n_stages = min((uint32_t)kMaxStages, (kDynBytes - off) / ((uint32_t)kTile * 4u)); // >= 4
     // ---- set-up -------------------------------------------------------------------------------------------------
-    if (a.timing && tid == 0)
+    if (a.timing && tid == 0 && !early)
         a.timing[(size_t)row * 64 + 0] = global_ns();
+    const unsigned long long t_begin = (a.timing && tid == 0 && early) ? global_ns() : 0ull;
     if (tid == 0) {
         for (int i = 0; i < kMaxStages; ++i) {
             mbar_init(&s.full[i], 1);
@@ -817,10 +789,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         s.hi_group = 0;
         s.n_final = 0;
         s.flags = 0;
+        s.n_distinct = 0;
         fence_barrier_init();
     }
-    uint32_t* const cnt = bitmap; // long histories: per-tile id counters (two 16-bit counters per word)
-    if (long_history)
+    uint32_t* const cnt = bitmap; // tile_fix: per-tile id counters (two 16-bit counters per word)
+    if (tile_fix)
         for (uint32_t i = tid; i < kTile / 2; i += kThreads)
             cnt[i] = 0;
     if (cfg.hist_mode)
@@ -832,36 +805,38 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                                        reinterpret_cast<unsigned char*>(bitmap)) / 16u;
         for (uint32_t i = tid; i < nz; i += kThreads)
             z[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (use_bias)
+            for (uint32_t i = tid; i < (uint32_t)kHistCap; i += kThreads)
+                biasval[i] = kNoBias;
     }
-    uint32_t tiles_issued = 0;
     __syncthreads();
-    if (a.timing && tid == 0)
+    if (a.timing && tid == 0 && !early)
         a.timing[(size_t)row * 64 + 6] = global_ns();
-    // The producer fills the ring before anything else, so that the copies fly during the set-up.
-    if (a.use_bulk_copy) {
-        tiles_issued = min(n_stages, n_tiles);
-        if (tid == 0) {
-            for (uint32_t t = 0; t < tiles_issued; ++t) {
-                const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
-                const uint32_t bytes = (n_t * 4u) & ~15u;
-                const float* src = lrow + (size_t)t * kTile;
-                for (uint32_t e = bytes / 4; e < n_t; ++e)
-                    ring[t * kTile + e] = src[e];
-                if (bytes > 0) {
-                    mbar_arrive_expect_tx(&s.full[t], bytes);
-                    bulk_load(ring + t * kTile, src, bytes, &s.full[t]);
-                } else {
-                    mbar_arrive(&s.full[t]);
-                }
+    // The producer fills the ring before anything else, so that the copies fly during the set-up (unless the set-up
+    // runs ahead of the previous kernel: then the logits come after the wait below).
+    const uint32_t tiles_issued = a.use_bulk_copy ? min(n_stages, n_tiles) : 0u;
+    auto fill_ring = [&]() {
+        for (uint32_t t = 0; t < tiles_issued; ++t) {
+            const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
+            const uint32_t bytes = (n_t * 4u) & ~15u;
+            const float* src = lrow + (size_t)t * kTile;
+            for (uint32_t e = bytes / 4; e < n_t; ++e)
+                ring[t * kTile + e] = src[e];
+            if (bytes > 0) {
+                mbar_arrive_expect_tx(&s.full[t], bytes);
+                bulk_load(ring + t * kTile, src, bytes, &s.full[t]);
+            } else {
+                mbar_arrive(&s.full[t]);
             }
         }
-    }
+    };
+    if (!early && tid == 0)
+        fill_ring();
     uint32_t own = 0; // this thread's history entries that were the first to name their column
     if (use_table) {
-        // The generated tokens as the reference keeps them (a multiset id -> count, sampler.cpp:15-18), in a form
-        // the readers can consult per column without searching: a bitmap of generated columns, the number of set
-        // bits before each bitmap word (so a column's rank among the distinct ones is one popcount away), and the
-        // counts by rank.
+        // The special columns as a bitmap: all the readers need in order to set them aside. The rest of what the
+        // reference keeps about the generated tokens (a multiset id -> count, sampler.cpp:15-18) is built by the
+        // side warps while the row already streams.
 #pragma unroll
         for (int hi = 0; hi < kHistPerThread; ++hi) {
             if (hc[hi] < V) { // unsigned: an id below the row's first column wraps past V
@@ -871,30 +846,69 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         own |= 1u << hi; // exactly one entry per distinct column sees its bit go from 0 to 1
             }
         }
+        for (uint32_t j = tid; j < nb; j += kThreads) {
+            const int32_t id = brow[j].id;
+            const int64_t loc = (int64_t)id - a.id_offset;
+            if (id >= 0 && loc >= 0 && loc < (int64_t)V)
+                atomicOr(&bitmap[(uint32_t)loc >> 5], 1u << ((uint32_t)loc & 31u));
+        }
         __syncthreads();
-        if (a.timing && tid == 0)
+        if (a.timing && tid == 0 && !early)
             a.timing[(size_t)row * 64 + 7] = global_ns();
+        // The rest of what the reference keeps about the generated tokens (a multiset id -> count,
+        // sampler.cpp:15-18) in a form that needs no search: the number of set bits before each bitmap word (so a
+        // column's rank among the special ones is one popcount away) and, by rank, how often the token occurs and
+        // its bias.
         word_ranks(s, bitmap, wpre, bm_words);
         __syncthreads();
-        if (a.timing && tid == 0)
+        if (a.timing && tid == 0 && !early)
             a.timing[(size_t)row * 64 + 8] = global_ns();
+        // (ranks of all of a thread's entries first, so that their look-ups are in flight together; then the adds)
+        {
+            uint32_t rk[kHistPerThread];
 #pragma unroll
-        for (int hi = 0; hi < kHistPerThread; ++hi) {
-            if (hc[hi] < V) {
-                const uint32_t col = hc[hi];
-                const uint32_t rank = wpre[col >> 5] + __popc(bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
-                atomicAdd(&counts[rank >> 1], 1u << ((rank & 1u) * 16u));
+            for (int hi = 0; hi < kHistPerThread; ++hi) {
+                const uint32_t col = hc[hi] < V ? hc[hi] : 0u;
+                rk[hi] = wpre[col >> 5] + __popc(bitmap[col >> 5] & ((1u << (col & 31u)) - 1u));
+            }
+#pragma unroll
+            for (int hi = 0; hi < kHistPerThread; ++hi)
+                if (hc[hi] < V)
+                    atomicAdd(&counts[rk[hi] >> 1], 1u << ((rk[hi] & 1u) * 16u));
+        }
+        for (uint32_t j = tid; j < nb; j += kThreads) {
+            const mk_bias be = brow[j];
+            const int64_t loc = (int64_t)be.id - a.id_offset;
+            if (be.id >= 0 && loc >= 0 && loc < (int64_t)V) {
+                const uint32_t col = (uint32_t)loc;
+                biasval[wpre[col >> 5] + __popc(bitmap[col >> 5] & ((1u << (col & 31u)) - 1u))] =
+                    __float_as_uint(be.value);
             }
         }
         __syncthreads();
-        if (a.timing && tid == 0)
+        if (a.timing && tid == 0 && !early)
             a.timing[(size_t)row * 64 + 4] = global_ns();
     }
-    // The tiles that were requested before the set-up have landed by now: all warps apply the sparse edits to them
-    // together (the first tiles hold the most frequent token ids, by far the largest share of the history), then
-    // the fix-up warps carry on alone with the tiles that follow.
+    if (early) {
+        griddep_wait();
+        if (tid == 0)
+            fill_ring();
+        if (a.timing && tid == 0) {
+            a.timing[(size_t)row * 64 + 0] = t_begin;
+            a.timing[(size_t)row * 64 + 7] = global_ns();
+        }
+    }
+    griddep_launch_dependents();
+    if (a.pass == 0 && tid == 0)
+        again[0] = 0u;
+    const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
+    const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
+    const int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
+    // The tiles that were requested before the set-up have landed by now (requested after the wait, they are waited
+    // for here): all warps edit their special columns together — the first tiles hold the most frequent token ids, by
+    // far the largest share of a history — then the fix-up warps carry on alone with the tiles that follow.
     uint32_t prefixed = 0;
-    if (has_fix && !long_history && tiles_issued > 0) {
+    if (use_table && tiles_issued > 0) {
         prefixed = tiles_issued;
         bool ok = true;
         for (uint32_t t = 0; t < prefixed; ++t)
@@ -913,31 +927,32 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
             __syncthreads();
         }
-        if (use_table) {
+        if (has_hist) {
             // Every column has one owner among the history entries (the one that set its bitmap bit); the owner
-            // applies the penalties. No search, no atomics: the entry names the column. Written as passes over
-            // the thread's entries, so that the shared-memory reads of all of them are in flight together.
-            float* const ring0 = ring;
-            uint32_t pc[kHistPerThread], pn[kHistPerThread];
+            // applies the penalties: no search, the entry names the column and its rank is at hand. Written as
+            // passes over the thread's entries, so that the shared-memory reads of all of them are in flight together.
+            uint32_t pn[kHistPerThread];
             float pv[kHistPerThread];
 #pragma unroll
             for (int hi = 0; hi < kHistPerThread; ++hi) {
-                const uint32_t col = hc[hi];
-                pc[hi] = (((own >> hi) & 1u) && col < span) ? col : 0xffffffffu;
-                const uint32_t c = (pc[hi] != 0xffffffffu) ? col : 0u;
+                const bool mine = ((own >> hi) & 1u) && hc[hi] < span;
+                hc[hi] = mine ? hc[hi] : 0xffffffffu;
+                const uint32_t c = mine ? hc[hi] : 0u;
                 pn[hi] = wpre[c >> 5] + __popc(bitmap[c >> 5] & ((1u << (c & 31u)) - 1u)); // rank
-                pv[hi] = ring0[c];
+                pv[hi] = ring[c];
             }
 #pragma unroll
             for (int hi = 0; hi < kHistPerThread; ++hi)
                 pn[hi] = (counts[pn[hi] >> 1] >> ((pn[hi] & 1u) * 16u)) & 0xffffu; // count
 #pragma unroll
-            for (int hi = 0; hi < kHistPerThread; ++hi) {
-                const float v = penalise(pv[hi], pn[hi], cfg);
-                if (pc[hi] != 0xffffffffu)
-                    ring0[pc[hi]] = v;
-            }
+            for (int hi = 0; hi < kHistPerThread; ++hi)
+                if (hc[hi] != 0xffffffffu)
+                    ring[hc[hi]] = penalise(pv[hi], pn[hi], cfg);
         }
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 20] = global_ns();
+        if (a.timing && tid == kThreads - 1)
+            a.timing[(size_t)row * 64 + 21] = global_ns();
         __syncthreads();
     }
     // ---- streaming ----------------------------------------------------------------------------------------------
@@ -994,22 +1009,67 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
         }
     } else if (warp <= kFixers / 32) {
-        // fix-up: each of the two warps owns every other tile (a long history: warp 0 owns them all, because its
-        // per-tile counters are shared), so two tiles are edited at a time and nothing synchronises across warps
-        if (has_fix) {
+        if (use_table) {
+            // fix-up warps: each owns every other tile. A lane takes the 128 columns of four consecutive bitmap words
+            // (one 128-bit load, and one 64-bit load for their ranks) and walks the set bits: the rank counts up from
+            // the first word's, the count and the bias are one look-up each, the edit is bias, then the penalties
+            // (sampler.cpp:23-28). Nothing synchronises across the two warps.
             const uint32_t fw = warp - 1;
             if (fw == 0 && lane == 0)
                 for (uint32_t t = 0; t < prefixed; ++t) // edited by all warps above
                     mbar_arrive(&s.ready[t]);
-            const uint32_t t_step = long_history ? 1u : (uint32_t)(kFixers / 32);
-            uint32_t t_first = prefixed;
-            if (!long_history)
-                t_first += (fw + (kFixers / 32) - (prefixed % (kFixers / 32))) % (kFixers / 32); // t % 2 == fw
-            const bool idle = long_history && fw != 0;
+            constexpr uint32_t kFixWarps = kFixers / 32;
+            uint32_t t_first = prefixed + (fw + kFixWarps - (prefixed % kFixWarps)) % kFixWarps; // t % 2 == fw
             uint32_t st = t_first % n_stages, k = t_first / n_stages;
-            for (uint32_t t = t_first; t < n_tiles && !idle; t += t_step, st += t_step) {
+            for (uint32_t t = t_first; t < n_tiles; t += kFixWarps, st += kFixWarps) {
                 if (st >= n_stages) {
                     st -= n_stages;
+                    ++k;
+                }
+                float* const tp = ring + st * kTile;
+                const uint32_t base = t * kTile;
+                const uint32_t w0 = (base >> 5) + lane * 4u;
+                // the words and their ranks do not depend on the tile's data: fetched before the wait
+                uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                uint32_t rank = 0;
+                if (w0 < bm_words) { // the bitmap is zero-padded to whole groups of four words
+                    x = *reinterpret_cast<const uint4*>(bitmap + w0);
+                    rank = (uint32_t)wpre[w0];
+                }
+                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
+                    atomicExch(&s.abort_flag, 1u);
+                const uint32_t wd[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t bits = wd[q];
+                    float* const tq = tp + lane * 128u + (uint32_t)q * 32u;
+                    while (bits) {
+                        const uint32_t bpos = (uint32_t)__ffs((int)bits) - 1u;
+                        bits &= bits - 1u;
+                        float v = tq[bpos];
+                        if (use_bias) {
+                            const uint32_t bv = biasval[rank];
+                            if (bv != kNoBias)
+                                v = __fadd_rn(v, __uint_as_float(bv));
+                        }
+                        const uint32_t n = (counts[rank >> 1] >> ((rank & 1u) * 16u)) & 0xffffu;
+                        if (n)
+                            v = penalise(v, n, cfg);
+                        tq[bpos] = v;
+                        ++rank;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&s.ready[st]);
+            }
+        } else if (tile_fix && warp == 1) {
+            // fix-up warp of the slow path: edits every tile in shared memory before the readers see it — bias, then
+            // the penalties of the tile's generated columns.
+            uint32_t st = 0, k = 0;
+            for (uint32_t t = 0; t < n_tiles; ++t, ++st) {
+                if (st == n_stages) {
+                    st = 0;
                     ++k;
                 }
                 float* tp = ring + st * kTile;
@@ -1026,13 +1086,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     }
                     __syncwarp();
                 }
-                if (use_table) {
-                    const uint32_t w_lo = base >> 5, w_hi = min((base + n_t + 31u) >> 5, bm_words);
-                    fix_hits(bitmap, wpre, counts, tp, base, w_lo, w_hi, (uint32_t)wpre[w_lo],
-                             (w_hi < bm_words) ? (uint32_t)wpre[w_hi] : s.n_distinct, lane, 32u, cfg);
-                } else if (has_hist) {
-                    // long history: count the tile's ids in 16-bit counters, then the first lane to clear a
-                    // counter owns that id and applies the penalties with its count
+                if (has_hist) {
+                    // count the tile's ids in 16-bit counters, then the first lane to clear a counter owns that id
+                    // and applies the penalties with its count
                     for (uint32_t j = lane; j < hlen; j += 32) {
                         const int64_t loc = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
                         if (loc >= 0 && loc < (int64_t)n_t)
@@ -1059,7 +1115,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // readers
         const uint32_t rt = tid - kProducerThreads - kFixers;
         const uint32_t rwarp = rt >> 5;
-        uint64_t* const avail = has_fix ? s.ready : s.full;
+        uint64_t* const avail = has_special ? s.ready : s.full;
         const float c2 = cfg.inv_t * 1.4426950408889634f;
         const float ninf = -__int_as_float(0x7f800000);
         const bool collect = !cfg.greedy || a.mode == kModeVpLocal;
@@ -1158,9 +1214,31 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
                     // where the count from the top reaches k bounds the k-th largest from below.
                     thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
-                    if (tm >= thr) {
-                        // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
-                        // valid one too (bounds only rise), and one pass over the 16 elements costs half of two
+                    const bool some = tm >= thr;
+                    const uint32_t lanes = __ballot_sync(0xffffffffu, some);
+                    // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
+                    // valid one too (bounds only rise), and one pass over the 16 elements costs half of two. While
+                    // the bound is still low (the first tiles of a row) most lanes keep something: the warp then
+                    // takes one slot range with a single atomic instead of one atomic per element on the same word.
+                    const bool together = collect && __popc(lanes) >= 8;
+                    uint32_t slot_w = 0;
+                    if (together) {
+                        uint32_t mine = 0;
+#pragma unroll
+                        for (int e = 0; e < kEl; ++e)
+                            mine += (w[e] >= thr) ? 1u : 0u;
+                        uint32_t inc = mine;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+                            if ((int)lane >= o)
+                                inc += y;
+                        }
+                        if (lane == 31)
+                            slot_w = atomicAdd(&s.ncand, inc);
+                        slot_w = __shfl_sync(0xffffffffu, slot_w, 31) + inc - mine;
+                    }
+                    if (some) {
                         uint32_t top_bin = 0;
 #pragma unroll
                         for (int e = 0; e < kEl; ++e)
@@ -1169,7 +1247,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                                 atomicAdd(&hist[bin], 1u);
                                 top_bin = max(top_bin, bin);
                                 if (collect) {
-                                    const uint32_t slot = atomicAdd(&s.ncand, 1u);
+                                    const uint32_t slot = together ? slot_w++ : atomicAdd(&s.ncand, 1u);
                                     if (slot < a.scratch_cap)
                                         scratch[slot] = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
                                 }
@@ -1215,15 +1293,48 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
                     sum_acc += (double)p;
                 }
-                if (!(kHist && cfg.hist_mode) && collect && tm >= thr) {
+                if (!(kHist && cfg.hist_mode) && collect) {
+                    const bool some = tm >= thr;
+                    const uint32_t lanes = __ballot_sync(0xffffffffu, some);
+                    if (__popc(lanes) >= 8) {
+                        // Many lanes have something to keep (a flat row, or the first tiles of any row, before the
+                        // maximum is known): one slot range per warp — a prefix sum over the lanes' counts and one
+                        // atomic — instead of one atomic per element on the same shared-memory word.
+                        uint32_t mine = 0;
 #pragma unroll
-                    for (int e = 0; e < kEl; ++e)
-                        if (w[e] >= thr) {
-                            const uint32_t slot = atomicAdd(&s.ncand, 1u);
-                            const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-                            if (slot < a.scratch_cap)
-                                scratch[slot] = c;
+                        for (int e = 0; e < kEl; ++e)
+                            mine += (w[e] >= thr) ? 1u : 0u;
+                        uint32_t inc = mine;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+                            if ((int)lane >= o)
+                                inc += y;
                         }
+                        uint32_t slot = 0;
+                        if (lane == 31)
+                            slot = atomicAdd(&s.ncand, inc);
+                        slot = __shfl_sync(0xffffffffu, slot, 31) + inc - mine;
+                        if (some) {
+#pragma unroll
+                            for (int e = 0; e < kEl; ++e)
+                                if (w[e] >= thr) {
+                                    if (slot < a.scratch_cap)
+                                        scratch[slot] = make_uint2(__float_as_uint(w[e]),
+                                                                   base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                                    ++slot;
+                                }
+                        }
+                    } else if (some) {
+#pragma unroll
+                        for (int e = 0; e < kEl; ++e)
+                            if (w[e] >= thr) {
+                                const uint32_t slot = atomicAdd(&s.ncand, 1u);
+                                const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                                if (slot < a.scratch_cap)
+                                    scratch[slot] = c;
+                            }
+                    }
                 }
             }
         };
@@ -1279,7 +1390,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         if (warp > kFixers / 32) {
             const float c2 = cfg.inv_t * 1.4426950408889634f;
             if (best > -__int_as_float(0x7f800000) && sum_acc > 0.0)
-                part = sum_acc * exp2((double)(best - m) * (double)c2);
+                part += sum_acc * exp2((double)(best - m) * (double)c2);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1)
                 part += __shfl_xor_sync(0xffffffffu, part, o);
@@ -1361,6 +1472,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
 
     // exact weights of the collected elements, min_p filter (sampler.cpp:33-35)
+    if (a.timing && tid == 0)
+        a.timing[(size_t)row * 64 + 22] = global_ns();
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
     const uint32_t n_raw = min(s.ncand, a.scratch_cap);
     bool overflow = s.ncand > a.scratch_cap;
@@ -1398,6 +1511,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
         }
+        if (a.timing && tid == 0)
+            a.timing[(size_t)row * 64 + 23] = global_ns();
         if (cfg.need_sum) {
             // top_p's total (sampler.cpp:45-47) covers every column: exact weights for all that was collected, the
             // approximate sum for the rest. The margin that goes with it is 1e-5 of the approximate part plus the
@@ -1745,10 +1860,21 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     }
     if (batch == 0)
         return cudaSuccess;
+    // With an overlap mode the launch carries the programmatic-serialization attribute: the grid may be scheduled
+    // while the previous kernel of the stream drains, and synchronises with it by griddep_wait() in the kernel.
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(batch);
+    lc.blockDim = dim3(kThreads);
+    lc.dynamicSmemBytes = kSmemBytes;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = a.overlap != MK_OVERLAP_OFF ? 1u : 0u;
     RowKernelArgs first = a;
     first.pass = 0;
-    row_pipeline_kernel<<<batch, kThreads, kSmemBytes, stream>>>(first);
-    e = cudaGetLastError();
+    e = cudaLaunchKernelEx(&lc, row_pipeline_kernel, first);
     if (e != cudaSuccess)
         return e;
     // top_p alone (make_cfg: need_sum): rows whose nucleus the first launch could not settle are streamed again
@@ -1760,8 +1886,7 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     if (a.mode != kModeVpLocal && kNucleusGuess < a.n_vocab && (a.params_dev || host_need_sum)) {
         RowKernelArgs second = a;
         second.pass = 1;
-        row_pipeline_kernel<<<batch, kThreads, kSmemBytes, stream>>>(second);
-        e = cudaGetLastError();
+        e = cudaLaunchKernelEx(&lc, row_pipeline_kernel, second);
     }
     return e;
 }

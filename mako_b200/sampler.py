@@ -121,6 +121,12 @@ class BatchSampler:
             lib.mk_sampler_destroy(h)
             self._h = None
 
+    def set_overlap(self, mode: int) -> None:
+        """How the row kernel is launched behind the previous kernel of the stream (mk_sampler_set_overlap):
+        0 plain stream order, 1 programmatic dependent launch, 2 the same with the per-row history tables built
+        before the wait (the caller promises that the previous kernel writes no parameters, histories or biases)."""
+        check(lib.mk_sampler_set_overlap(self._h, int(mode)))
+
     # -- argument marshalling -----------------------------------------------------------------------------------
     def _rows(self, logits: torch.Tensor, params, history=None, history_len=None, mask=None, bias=None,
               n_vocab=None, id_offset: int = 0) -> RowsC:

@@ -197,3 +197,42 @@ def test_second_pass_only_for_rows_that_ask(gpu_sampler_factory, ref):
     g2 = inp2.to_gpu()
     res = s.sample(g2["logits"], p, g2["u"], **g2["kw"])
     compare_sample(res, oracle_sample_rows(ref, p, inp2, cap=cap), cap=cap)
+
+
+def test_overlap_modes_give_the_same_tokens(gpu_sampler_factory, ref):
+    """Back-to-back launches behind one another with programmatic dependent launch, with and without the history
+    tables built ahead of the wait, replayed from a CUDA graph as well: the tokens are those of plain stream order
+    and of the CPU reference. The same handle (and so the same scratch) serves consecutive launches."""
+    import torch
+    from mako_b200 import BatchSampler
+    v, b, h = 40003, 24, 700
+    p = SamplingParams(temperature=0.8, top_p=0.9, min_p=0.05, repetition_penalty=1.1, presence_penalty=0.5,
+                       frequency_penalty=0.3)
+    sets = [Inputs(300 + k, b, v, n_history=h) for k in range(3)]
+    gs = [i.to_gpu() for i in sets]
+    want = [[ref.sample(p, i.logits[r], i.u[r], history=i.history[r])["token"] for r in range(b)] for i in sets]
+    s = BatchSampler(v, b, 0)
+    outs = [torch.empty(b, dtype=torch.int32, device="cuda") for _ in sets]
+    for mode in (0, 1, 2):
+        s.set_overlap(mode)
+        for k, g in enumerate(gs):                      # three launches in a row on the current stream
+            outs[k].copy_(s.sample(g["logits"], p, g["u"], **g["kw"]).token)
+        torch.cuda.synchronize()
+        for k in range(3):
+            assert outs[k].cpu().tolist() == want[k], f"overlap mode {mode}, launch {k}"
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for k, g in enumerate(gs):
+                outs[k].copy_(s.sample(g["logits"], p, g["u"], **g["kw"]).token)
+    torch.cuda.current_stream().wait_stream(side)
+    for o in outs:
+        o.zero_()
+    graph.replay()
+    graph.replay()
+    torch.cuda.synchronize()
+    for k in range(3):
+        assert outs[k].cpu().tolist() == want[k], f"graph replay, launch {k}"
+    s.set_overlap(0)

@@ -77,7 +77,8 @@ def test_uneven_shards_count_a_boundary_id_for_its_own_shard(gpu_sampler_factory
     v, n_shards, k, b = 151936, 8, 64, 2
     spans = [vocab_shard(v, g, n_shards) for g in range(n_shards)]
     assert spans[0] == (0, 19008) and spans[4][1] - spans[4][0] == 18976
-    logits = np.full((b, v), -30.0, dtype=np.float32)
+    # a spread-out background far below the heavy columns (identical values would all tie for a shard's list)
+    logits = np.random.default_rng(5).uniform(-1000.0, -30.0, size=(b, v)).astype(np.float32)
     logits[0, 19008 - 70:19008] = 10.0 - 0.001 * np.arange(70, dtype=np.float32)
     cols = np.concatenate([np.arange(lo + 5, lo + 15) for lo, _ in spans[:7]])
     logits[1, cols] = 10.0 - 0.001 * np.arange(70, dtype=np.float32)
