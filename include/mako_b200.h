@@ -259,6 +259,13 @@ int mk_debug_expf(const float* x_dev, float* y_dev, uint64_t n, void* stream);
  * the finish [11] candidates filtered ([9] collected, [10] kept: counts, not times), [12] ordered, [13] top_p done. */
 int mk_debug_set_timing(mk_sampler* s, unsigned long long* timing_dev);
 
+/* Test hook for the bounded waits: the following sample / verify launches of this handle never request the copy of
+ * tile `tile` (4096 columns each) of any row, and a wait for a tile gives up after `wait_probes` probes of up to
+ * 20 us each instead of after seconds. Every wait in the kernel is bounded: the waits for the missing tile run out,
+ * the row's CTA leaves in good order and the row reports token -1 with MK_FLAG_TIMEOUT — no trap, no hang, the
+ * context stays usable. tile < 0 switches the hook off (and wait_probes 0 restores the default limit). */
+int mk_debug_withhold_tile(mk_sampler* s, int tile, uint32_t wait_probes);
+
 /* Bytes the roofline counts for one row: logits once + history + mask + bias + uniforms + outputs. */
 uint64_t mk_row_bytes(uint32_t n_vocab, uint32_t n_history, int has_mask, uint32_t n_bias, uint32_t n_uniforms);
 

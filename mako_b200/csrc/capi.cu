@@ -58,6 +58,7 @@ struct mk_sampler {
     cudaStream_t own_stream = nullptr;
     int overlap = MK_OVERLAP_OFF;         // how the row kernel is launched behind its predecessor in the stream
     unsigned long long* timing = nullptr; // debug: per-row phase timestamps of the next launches
+    uint32_t skip_tile = 0xffffffffu, wait_probes = 0; // debug: withhold one tile's copy; probes before a wait gives up
     unsigned long long* pick_best = nullptr; // mk_draft_pick: one packed (score, id) maximum per sequence
     unsigned char* stage = nullptr;
     size_t stage_bytes = 0;
@@ -132,6 +133,8 @@ void fill_common(mk::RowKernelArgs& a, const mk_sampler* s, const mk_rows* r)
     a.scratch_cap = scratch_cap(s->n_vocab);
     a.timing = s->timing;
     a.overlap = s->overlap;
+    a.debug_skip_tile = s->skip_tile;
+    a.debug_wait_probes = s->wait_probes;
     a.use_bulk_copy = ((reinterpret_cast<uintptr_t>(r->logits) & 15u) == 0 && (r->ld % 4u) == 0) ? 1 : 0;
 }
 
@@ -625,6 +628,15 @@ int mk_sampler_set_overlap(mk_sampler* s, int mode)
     if (mode != MK_OVERLAP_OFF && mode != MK_OVERLAP_LAUNCH && mode != MK_OVERLAP_STABLE_SIDE_INPUTS)
         return fail(MK_ERR_INVALID_ARGUMENT, "overlap mode %d is none of MK_OVERLAP_*", mode);
     s->overlap = mode;
+    return MK_OK;
+}
+
+int mk_debug_withhold_tile(mk_sampler* s, int tile, uint32_t wait_probes)
+{
+    if (!s)
+        return fail(MK_ERR_INVALID_ARGUMENT, "null sampler handle");
+    s->skip_tile = tile < 0 ? 0xffffffffu : (uint32_t)tile;
+    s->wait_probes = wait_probes;
     return MK_OK;
 }
 

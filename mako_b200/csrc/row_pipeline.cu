@@ -59,6 +59,10 @@ constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
 constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) once the streaming is over
 constexpr uint32_t kBarSort = 3;         // named barrier of the sorting warps
 constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates kept
+#ifndef MK_PREFIX_TILES
+#define MK_PREFIX_TILES 4
+#endif
+constexpr int kPrefixTiles = MK_PREFIX_TILES;  // tiles all warps edit before the stream starts (their columns fit 16 bits)
 constexpr uint32_t kNoBias = 0x7fa00001u; // a NaN payload no caller's bias carries: this rank has no bias
 constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = 21;
@@ -81,6 +85,7 @@ struct __align__(128) Smem {
     uint32_t n_final;
     uint32_t flags;
     uint32_t n_distinct;            // distinct special columns (generated or biased)
+    uint32_t n_own;                 // generated columns within the first tiles (edited by all warps)
 };
 constexpr uint32_t kSmemBytes = 115712; // two CTAs per SM: (228 KB - 2 x 1 KB reserved) / 2
 constexpr uint32_t kHeadBytes = (sizeof(Smem) + 127u) & ~127u;
@@ -205,6 +210,54 @@ __device__ __forceinline__ unsigned long long pack_by_weight(float q, uint32_t c
 __device__ __forceinline__ unsigned long long pack_by_column(float q, uint32_t col)
 {
     return ((unsigned long long)col << 32) | __float_as_uint(q);
+}
+
+// Position of the n-th set bit (n = 0: the lowest) of a word that has more than n bits set: five halvings by
+// popcount (the library's find-n-th-set is a loop over the bits).
+__device__ __forceinline__ uint32_t nth_set_bit(uint32_t w, uint32_t n)
+{
+    uint32_t pos = 0;
+#pragma unroll
+    for (uint32_t width = 16; width > 0; width >>= 1) {
+        const uint32_t c = (uint32_t)__popc(w & ((1u << width) - 1u));
+        if (n >= c) {
+            n -= c;
+            pos += width;
+            w >>= width;
+        }
+    }
+    return pos;
+}
+
+// Penalties (sampler.cpp:23-28) for the generated columns with ranks [r_lo, r_hi) — the ones whose bitmap words lie
+// in [w_lo, w_hi) — spread evenly over n_thr threads (this one is `thr`): a rank is turned back into its column by a
+// binary search over the per-word ranks and a find-n-th-set-bit in the word, and indexes the count directly. Every
+// column is touched by exactly one thread. `tile` points at column `col0` of the row in shared memory.
+__device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t* wpre, const uint32_t* counts,
+                                         const uint32_t* biasval, float* tile, uint32_t col0, uint32_t w_lo,
+                                         uint32_t w_hi, uint32_t r_lo, uint32_t r_hi, uint32_t thr, uint32_t n_thr,
+                                         const RowCfg& cfg)
+{
+    for (uint32_t r = r_lo + thr; r < r_hi; r += n_thr) {
+        uint32_t lo = w_lo, hi = w_hi; // largest word in [lo, hi) whose rank is <= r
+        while (hi - lo > 1u) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if ((uint32_t)wpre[mid] <= r)
+                lo = mid;
+            else
+                hi = mid;
+        }
+        const uint32_t bit = nth_set_bit(bitmap[lo], r - (uint32_t)wpre[lo]);
+        const uint32_t n = (counts[r >> 1] >> ((r & 1u) * 16u)) & 0xffffu;
+        const uint32_t loc = (lo << 5) + bit - col0;
+        float v = tile[loc];
+        if (biasval) {
+            const uint32_t bv = biasval[r];
+            if (bv != kNoBias)
+                v = __fadd_rn(v, __uint_as_float(bv));
+        }
+        tile[loc] = n ? penalise(v, n, cfg) : v;
+    }
 }
 
 // Exclusive prefix of the per-word popcounts of bitmap[0, bm_words) into wpre, total into s.n_distinct: a set
@@ -704,6 +757,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // ahead and only the logits, the mask, the uniforms and every write to global memory wait. The second pass reads
     // a word the first pass wrote: it always waits first.
     const bool early = a.overlap == MK_OVERLAP_STABLE_SIDE_INPUTS && a.pass == 0;
+    // Probes a wait for a tile makes before it gives up (each parks the thread for up to 20 us): seconds normally, a
+    // few milliseconds with the test hook that withholds a tile.
+    const uint32_t wait_probes = a.debug_wait_probes ? a.debug_wait_probes : (1u << 17);
     if (!early)
         griddep_wait();
     const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
@@ -790,6 +846,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         s.n_final = 0;
         s.flags = 0;
         s.n_distinct = 0;
+        s.n_own = 0;
         fence_barrier_init();
     }
     uint32_t* const cnt = bitmap; // tile_fix: per-tile id counters (two 16-bit counters per word)
@@ -813,10 +870,15 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (a.timing && tid == 0 && !early)
         a.timing[(size_t)row * 64 + 6] = global_ns();
     // The producer fills the ring before anything else, so that the copies fly during the set-up (unless the set-up
-    // runs ahead of the previous kernel: then the logits come after the wait below).
+    // runs ahead of the previous kernel: then the logits come after the wait below). With a history the last stage
+    // first serves the set-up as a list (see below) and is requested once that list has been used.
     const uint32_t tiles_issued = a.use_bulk_copy ? min(n_stages, n_tiles) : 0u;
-    auto fill_ring = [&]() {
-        for (uint32_t t = 0; t < tiles_issued; ++t) {
+    const bool list_owners = use_table && has_hist && tiles_issued > 0;
+    const uint32_t tiles_early = (list_owners && tiles_issued == n_stages) ? n_stages - 1u : tiles_issued;
+    auto fill_ring = [&](uint32_t t0, uint32_t t1) {
+        for (uint32_t t = t0; t < t1; ++t) {
+            if (t == a.debug_skip_tile)
+                continue; // test hook: this tile's copy is never requested, so that the waits for it run out
             const uint32_t n_t = min((uint32_t)kTile, V - t * kTile);
             const uint32_t bytes = (n_t * 4u) & ~15u;
             const float* src = lrow + (size_t)t * kTile;
@@ -831,19 +893,34 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
     };
     if (!early && tid == 0)
-        fill_ring();
-    uint32_t own = 0; // this thread's history entries that were the first to name their column
+        fill_ring(0, tiles_early);
+    // The first tiles hold the most frequent token ids, by far the largest share of a history: all warps edit
+    // their generated columns together before the stream starts. The columns to edit are listed while the bitmap is
+    // built — by the history entry that sets a column's bit, so each column once — in the last ring stage.
+    const uint32_t prefixed = list_owners ? min((uint32_t)kPrefixTiles, tiles_early) : 0u;
+    const uint32_t span = min(prefixed * (uint32_t)kTile, V);
+    uint16_t* const own_list = reinterpret_cast<uint16_t*>(ring + (n_stages - 1u) * kTile); // <= kHistCap entries
     if (use_table) {
         // The special columns as a bitmap: all the readers need in order to set them aside. The rest of what the
         // reference keeps about the generated tokens (a multiset id -> count, sampler.cpp:15-18) is built by the
         // side warps while the row already streams.
 #pragma unroll
         for (int hi = 0; hi < kHistPerThread; ++hi) {
+            bool mine = false;
             if (hc[hi] < V) { // unsigned: an id below the row's first column wraps past V
                 const uint32_t col = hc[hi], bit = 1u << (col & 31u);
                 if (!(*(volatile uint32_t*)&bitmap[col >> 5] & bit)) // skip the atomic once the bit is visible
                     if (!(atomicOr(&bitmap[col >> 5], bit) & bit))
-                        own |= 1u << hi; // exactly one entry per distinct column sees its bit go from 0 to 1
+                        mine = col < span; // exactly one entry per distinct column sees its bit go from 0 to 1
+            }
+            const uint32_t bal = __ballot_sync(0xffffffffu, mine);
+            if (bal) { // one slot range per warp and round
+                uint32_t at = 0;
+                if (lane == 0)
+                    at = atomicAdd(&s.n_own, (uint32_t)__popc(bal));
+                at = __shfl_sync(0xffffffffu, at, 0) + (uint32_t)__popc(bal & ((1u << lane) - 1u));
+                if (mine)
+                    own_list[at] = (uint16_t)hc[hi];
             }
         }
         for (uint32_t j = tid; j < nb; j += kThreads) {
@@ -892,7 +969,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (early) {
         griddep_wait();
         if (tid == 0)
-            fill_ring();
+            fill_ring(0, tiles_early);
         if (a.timing && tid == 0) {
             a.timing[(size_t)row * 64 + 0] = t_begin;
             a.timing[(size_t)row * 64 + 7] = global_ns();
@@ -904,20 +981,16 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
     const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
     const int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
-    // The tiles that were requested before the set-up have landed by now (requested after the wait, they are waited
-    // for here): all warps edit their special columns together — the first tiles hold the most frequent token ids, by
-    // far the largest share of a history — then the fix-up warps carry on alone with the tiles that follow.
-    uint32_t prefixed = 0;
-    if (use_table && tiles_issued > 0) {
-        prefixed = tiles_issued;
+    if (prefixed > 0) {
+        // requested before the set-up, the first tiles have landed by now (requested after the wait, they are
+        // waited for here)
         bool ok = true;
         for (uint32_t t = 0; t < prefixed; ++t)
-            ok = mbar_wait(&s.full[t], 0) && ok;
+            ok = mbar_wait(&s.full[t], 0, wait_probes) && ok;
         if (!ok)
             atomicExch(&s.abort_flag, 1u);
         if (a.timing && tid == 0)
             a.timing[(size_t)row * 64 + 5] = global_ns();
-        const uint32_t span = min(prefixed * (uint32_t)kTile, V);
         if (nb > 0) {
             for (uint32_t j = tid; j < nb; j += kThreads) {
                 const mk_bias be = brow[j];
@@ -927,33 +1000,20 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
             __syncthreads();
         }
-        if (has_hist) {
-            // Every column has one owner among the history entries (the one that set its bitmap bit); the owner
-            // applies the penalties: no search, the entry names the column and its rank is at hand. Written as
-            // passes over the thread's entries, so that the shared-memory reads of all of them are in flight together.
-            uint32_t pn[kHistPerThread];
-            float pv[kHistPerThread];
-#pragma unroll
-            for (int hi = 0; hi < kHistPerThread; ++hi) {
-                const bool mine = ((own >> hi) & 1u) && hc[hi] < span;
-                hc[hi] = mine ? hc[hi] : 0xffffffffu;
-                const uint32_t c = mine ? hc[hi] : 0u;
-                pn[hi] = wpre[c >> 5] + __popc(bitmap[c >> 5] & ((1u << (c & 31u)) - 1u)); // rank
-                pv[hi] = ring[c];
-            }
-#pragma unroll
-            for (int hi = 0; hi < kHistPerThread; ++hi)
-                pn[hi] = (counts[pn[hi] >> 1] >> ((pn[hi] & 1u) * 16u)) & 0xffffu; // count
-#pragma unroll
-            for (int hi = 0; hi < kHistPerThread; ++hi)
-                if (hc[hi] != 0xffffffffu)
-                    ring[hc[hi]] = penalise(pv[hi], pn[hi], cfg);
+        // no search: the list names the column, its rank is one popcount away and indexes the count
+        const uint32_t n_own = s.n_own;
+#pragma unroll 2
+        for (uint32_t i = tid; i < n_own; i += kThreads) {
+            const uint32_t c = own_list[i];
+            const uint32_t rank = wpre[c >> 5] + __popc(bitmap[c >> 5] & ((1u << (c & 31u)) - 1u));
+            const uint32_t n = (counts[rank >> 1] >> ((rank & 1u) * 16u)) & 0xffffu;
+            ring[c] = penalise(ring[c], n, cfg);
         }
-        if (a.timing && tid == 0)
-            a.timing[(size_t)row * 64 + 20] = global_ns();
-        if (a.timing && tid == kThreads - 1)
-            a.timing[(size_t)row * 64 + 21] = global_ns();
         __syncthreads();
+    }
+    if (tid == 0 && tiles_issued > tiles_early) {
+        fence_proxy_async(); // the stage was written as plain shared memory until here
+        fill_ring(tiles_early, tiles_issued);
     }
     // ---- streaming ----------------------------------------------------------------------------------------------
     if (a.timing && tid == 0)
@@ -987,6 +1047,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
             if (*(volatile uint32_t*)&s.abort_flag)
                 break;
+            if (t == a.debug_skip_tile)
+                continue;
             if (a.use_bulk_copy) {
                 if (lane == 0) {
                     fence_proxy_async();
@@ -1010,55 +1072,29 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
     } else if (warp <= kFixers / 32) {
         if (use_table) {
-            // fix-up warps: each owns every other tile. A lane takes the 128 columns of four consecutive bitmap words
-            // (one 128-bit load, and one 64-bit load for their ranks) and walks the set bits: the rank counts up from
-            // the first word's, the count and the bias are one look-up each, the edit is bias, then the penalties
-            // (sampler.cpp:23-28). Nothing synchronises across the two warps.
+            // fix-up warps: each owns every other tile of those that follow the ones edited above. The tile's generated
+            // columns are spread evenly over the lanes by rank: a rank is turned back into its column by a binary
+            // search over the per-word ranks and a find-n-th-set-bit, and indexes count and bias directly; the edit is
+            // bias, then the penalties (sampler.cpp:23-28). Nothing synchronises across the two warps.
             const uint32_t fw = warp - 1;
+            constexpr uint32_t kFixWarps = kFixers / 32;
             if (fw == 0 && lane == 0)
                 for (uint32_t t = 0; t < prefixed; ++t) // edited by all warps above
                     mbar_arrive(&s.ready[t]);
-            constexpr uint32_t kFixWarps = kFixers / 32;
-            uint32_t t_first = prefixed + (fw + kFixWarps - (prefixed % kFixWarps)) % kFixWarps; // t % 2 == fw
+            const uint32_t t_first = prefixed + (fw + kFixWarps - (prefixed % kFixWarps)) % kFixWarps; // t % 2 == fw
             uint32_t st = t_first % n_stages, k = t_first / n_stages;
             for (uint32_t t = t_first; t < n_tiles; t += kFixWarps, st += kFixWarps) {
                 if (st >= n_stages) {
                     st -= n_stages;
                     ++k;
                 }
-                float* const tp = ring + st * kTile;
-                const uint32_t base = t * kTile;
-                const uint32_t w0 = (base >> 5) + lane * 4u;
-                // the words and their ranks do not depend on the tile's data: fetched before the wait
-                uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                uint32_t rank = 0;
-                if (w0 < bm_words) { // the bitmap is zero-padded to whole groups of four words
-                    x = *reinterpret_cast<const uint4*>(bitmap + w0);
-                    rank = (uint32_t)wpre[w0];
-                }
-                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
+                const uint32_t base = t * kTile, n_t = min((uint32_t)kTile, V - base);
+                const uint32_t w_lo = base >> 5, w_hi = min((base + n_t + 31u) >> 5, bm_words);
+                const uint32_t r_lo = (uint32_t)wpre[w_lo], r_hi = (w_hi < bm_words) ? (uint32_t)wpre[w_hi] : s.n_distinct;
+                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : wait_probes))
                     atomicExch(&s.abort_flag, 1u);
-                const uint32_t wd[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t bits = wd[q];
-                    float* const tq = tp + lane * 128u + (uint32_t)q * 32u;
-                    while (bits) {
-                        const uint32_t bpos = (uint32_t)__ffs((int)bits) - 1u;
-                        bits &= bits - 1u;
-                        float v = tq[bpos];
-                        if (use_bias) {
-                            const uint32_t bv = biasval[rank];
-                            if (bv != kNoBias)
-                                v = __fadd_rn(v, __uint_as_float(bv));
-                        }
-                        const uint32_t n = (counts[rank >> 1] >> ((rank & 1u) * 16u)) & 0xffffu;
-                        if (n)
-                            v = penalise(v, n, cfg);
-                        tq[bpos] = v;
-                        ++rank;
-                    }
-                }
+                fix_hits(bitmap, wpre, counts, use_bias ? biasval : nullptr, ring + st * kTile, base, w_lo, w_hi, r_lo,
+                         r_hi, lane, 32u, cfg);
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&s.ready[st]);
@@ -1075,7 +1111,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 float* tp = ring + st * kTile;
                 const uint32_t base = t * kTile;
                 const uint32_t n_t = min((uint32_t)kTile, V - base);
-                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
+                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : wait_probes))
                     atomicExch(&s.abort_flag, 1u);
                 if (nb > 0) {
                     for (uint32_t j = lane; j < nb; j += 32) {
@@ -1125,9 +1161,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // compiled in or out: a row runs a variant that holds little beyond its own work. (One loop with all
         // three as run-time branches costs the common penalised row 12 % of its launch time, and all eight
         // combinations cost it 3 % again: the size of the code matters, executed or not.)
-        auto read_tiles = [&](auto has_mask, auto has_hist, auto has_sum) {
+        auto read_tiles = [&](auto has_mask, auto has_hist, auto has_sum, auto aggregate) {
             constexpr bool kMask = decltype(has_mask)::value, kHist = decltype(has_hist)::value,
-                           kSum = decltype(has_sum)::value;
+                           kSum = decltype(has_sum)::value, kAgg = decltype(aggregate)::value;
             uint32_t mw_next[kVec];
 #pragma unroll
             for (int j = 0; j < kVec; ++j) {
@@ -1152,7 +1188,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         mw_next[j] = (i0 < V) ? __ldg(mrow + (i0 >> 5)) : 0u;
                     }
                 }
-                if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : (1u << 17)))
+                if (!mbar_wait(&avail[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : wait_probes))
                     atomicExch(&s.abort_flag, 1u); // keep walking: the named barriers below must stay matched
                 float w[kEl];
                 const float4* tp4 = reinterpret_cast<const float4*>(ring + st * kTile);
@@ -1214,31 +1250,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
                     // where the count from the top reaches k bounds the k-th largest from below.
                     thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
-                    const bool some = tm >= thr;
-                    const uint32_t lanes = __ballot_sync(0xffffffffu, some);
-                    // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
-                    // valid one too (bounds only rise), and one pass over the 16 elements costs half of two. While
-                    // the bound is still low (the first tiles of a row) most lanes keep something: the warp then
-                    // takes one slot range with a single atomic instead of one atomic per element on the same word.
-                    const bool together = collect && __popc(lanes) >= 8;
-                    uint32_t slot_w = 0;
-                    if (together) {
-                        uint32_t mine = 0;
-#pragma unroll
-                        for (int e = 0; e < kEl; ++e)
-                            mine += (w[e] >= thr) ? 1u : 0u;
-                        uint32_t inc = mine;
-#pragma unroll
-                        for (int o = 1; o < 32; o <<= 1) {
-                            const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
-                            if ((int)lane >= o)
-                                inc += y;
-                        }
-                        if (lane == 31)
-                            slot_w = atomicAdd(&s.ncand, inc);
-                        slot_w = __shfl_sync(0xffffffffu, slot_w, 31) + inc - mine;
-                    }
-                    if (some) {
+                    if (tm >= thr) {
+                        // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
+                        // valid one too (bounds only rise), and one pass over the 16 elements costs half of two
                         uint32_t top_bin = 0;
 #pragma unroll
                         for (int e = 0; e < kEl; ++e)
@@ -1247,7 +1261,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                                 atomicAdd(&hist[bin], 1u);
                                 top_bin = max(top_bin, bin);
                                 if (collect) {
-                                    const uint32_t slot = together ? slot_w++ : atomicAdd(&s.ncand, 1u);
+                                    const uint32_t slot = atomicAdd(&s.ncand, 1u);
                                     if (slot < a.scratch_cap)
                                         scratch[slot] = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
                                 }
@@ -1295,8 +1309,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
                 if (!(kHist && cfg.hist_mode) && collect) {
                     const bool some = tm >= thr;
-                    const uint32_t lanes = __ballot_sync(0xffffffffu, some);
-                    if (__popc(lanes) >= 8) {
+                    const uint32_t lanes = kAgg ? __ballot_sync(0xffffffffu, some) : 0u;
+                    if (kAgg && __popc(lanes) >= 8) {
                         // Many lanes have something to keep (a flat row, or the first tiles of any row, before the
                         // maximum is known): one slot range per warp — a prefix sum over the lanes' counts and one
                         // atomic — instead of one atomic per element on the same shared-memory word.
@@ -1341,13 +1355,15 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         using T = std::true_type;
         using F = std::false_type;
         if (!mrow && !cfg.hist_mode && !cfg.need_sum)
-            read_tiles(F{}, F{}, F{}); // penalties, min_p, greedy: nothing but maximum and bound
+            read_tiles(F{}, F{}, F{}, F{}); // penalties, min_p, greedy: nothing but maximum and bound
         else if (!mrow && !cfg.need_sum)
-            read_tiles(F{}, T{}, F{}); // top_k
+            read_tiles(F{}, T{}, F{}, F{}); // top_k
+        else if (!mrow && a.pass == 1)
+            read_tiles(F{}, F{}, T{}, T{}); // top_p alone, second pass: a third of a flat row is kept
         else if (!mrow)
-            read_tiles(F{}, T{}, T{}); // top_p alone (with its first-launch histogram), shard records
+            read_tiles(F{}, T{}, T{}, F{}); // top_p alone (with its first-launch histogram), shard records
         else
-            read_tiles(T{}, T{}, T{}); // masked rows: everything, chosen at run time
+            read_tiles(T{}, T{}, T{}, F{}); // masked rows: everything, chosen at run time
         if (best_col >= 0)
             atomicMax(&s.best_key,
                       ((unsigned long long)order_key(best) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)best_col));
@@ -1381,6 +1397,185 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     uint32_t flags = hlen_clamped ? MK_FLAG_HISTORY_FULL : 0u;
     if (mrow && !any_finite && !s.nan0)
         flags |= MK_FLAG_ALL_MASKED;
+
+    // ---- the short finish: what nearly every row takes ---------------------------------------------------------
+    // Few collected elements, at most 32 of them candidates, no row total beyond their own: one warp does it all in
+    // registers — exact weights, a 32-key sorting network over the lanes, top_k / top_p / total / draw as sequential
+    // chains fed by shuffles, in the reference's order and precision (sampler.cpp:33-73, 86-107) — while the other
+    // warps wait at one barrier. A one-shot phase waits for its instructions more than for anything else, so this path
+    // is short and contiguous; every other row falls through to the general finish below, which recomputes from the
+    // collected elements.
+    constexpr uint32_t kFastRaw = 256;
+    if (a.mode != kModeVpLocal && !cfg.greedy && !cfg.need_sum && !s.nan0 && s.ncand <= kFastRaw &&
+        s.ncand <= a.scratch_cap) {
+        if (warp == 0) {
+            const uint32_t full = 0xffffffffu;
+            const uint32_t n_raw = s.ncand;
+            const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
+            unsigned long long* const fkeys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
+            uint32_t n = 0;
+            uint2 craw[kFastRaw / 32]; // all requested at once: one trip to memory under load, not one per chunk
+#pragma unroll
+            for (uint32_t i = 0; i < kFastRaw / 32; ++i)
+                craw[i] = (i * 32u + lane < n_raw) ? scratch[i * 32u + lane] : make_uint2(0xff800000u, 0u);
+#pragma unroll
+            for (uint32_t i = 0; i < kFastRaw / 32; ++i) {
+                if (i * 32u >= n_raw || n > 32u)
+                    break;
+                const uint2 c = craw[i];
+                float q = 0.0f;
+                if (__uint_as_float(c.x) >= thr_final)
+                    q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
+                const bool ok = q >= cfg.minp_eff && q > 0.0f; // false for NaN
+                const uint32_t bal = __ballot_sync(full, ok);
+                const uint32_t pos = n + (uint32_t)__popc(bal & ((1u << lane) - 1u));
+                if (ok && pos < 32u)
+                    fkeys[pos] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
+                n += (uint32_t)__popc(bal);
+            }
+            __syncwarp();
+            if (n <= 32u) {
+                uint32_t fl = flags;
+                if (n == 0) { // sampler.cpp:37-38
+                    fl |= MK_FLAG_NO_CANDIDATE;
+                    if (lane == 0)
+                        fkeys[0] = ((unsigned long long)__float_as_uint(1.0f) << 32) | arg_col;
+                    n = 1;
+                    __syncwarp();
+                }
+                const bool cut_k = cfg.top_k > 0 && cfg.top_k < n; // sampler.cpp:39
+                const bool sorted = cut_k || cfg.use_topp;         // else ascending id
+                unsigned long long key = ~0ull;
+                if (lane < n) {
+                    const unsigned long long raw = fkeys[lane];
+                    const float q = __uint_as_float((uint32_t)(raw >> 32));
+                    const uint32_t col = (uint32_t)(raw & 0xffffffffull);
+                    key = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
+                }
+                for (uint32_t k = 2; k <= 32u; k <<= 1) // bitonic network over the 32 lanes
+                    for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+                        const unsigned long long other = __shfl_xor_sync(full, key, j);
+                        const bool keep_small = ((lane & j) == 0) == ((lane & k) == 0);
+                        key = (keep_small == (key < other)) ? key : other;
+                    }
+                float q;
+                uint32_t col;
+                if (sorted) {
+                    q = __uint_as_float(~(uint32_t)(key >> 32));
+                    col = (uint32_t)(key & 0xffffffffull);
+                } else {
+                    q = __uint_as_float((uint32_t)(key & 0xffffffffull));
+                    col = (uint32_t)(key >> 32);
+                }
+                if (lane >= n)
+                    q = 0.0f;
+                if (cut_k) { // sampler.cpp:40-42; the tie rule is the general finish's
+                    const float qk = __shfl_sync(full, q, (int)cfg.top_k - 1);
+                    const uint32_t edge_key = s.thr_topk_key;
+                    const float below = key_to_float(edge_key - 1u);
+                    if (edge_key > order_key(-FLT_MAX) &&
+                        expf_host_exact(__fmul_rn(__fsub_rn(below, m), cfg.inv_t)) >= qk)
+                        fl |= MK_FLAG_GUARD_BAND;
+                    n = cfg.top_k;
+                }
+                if (cfg.use_topp) { // sampler.cpp:44-61, sequentially
+                    double total_d = 0.0;
+                    for (uint32_t j = 0; j < n; ++j)
+                        total_d += (double)__shfl_sync(full, q, (int)j);
+                    const double band = 0x1p-40 * total_d, want = (double)cfg.top_p * total_d;
+                    double run = 0.0, prev = 0.0;
+                    uint32_t k = 0;
+                    for (uint32_t j = 0; j < n && run < want; ++j) {
+                        prev = run;
+                        run += (double)__shfl_sync(full, q, (int)j);
+                        k = j + 1u;
+                    }
+                    if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
+                        fl |= MK_FLAG_GUARD_BAND;
+                    n = max(k, 1u);
+                }
+                if (lane >= n)
+                    q = 0.0f;
+                float total = 0.0f;
+                for (uint32_t j = 0; j < n; ++j)
+                    total = __fadd_rn(total, __shfl_sync(full, q, (int)j));
+                const int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
+                const uint32_t dm = __ballot_sync(full, draft >= 0 && lane < n && (int32_t)col + a.id_offset == draft);
+                const uint32_t draft_idx = dm ? (uint32_t)__ffs((int)dm) - 1u : 0xffffffffu;
+                const float q_draft = dm ? __shfl_sync(full, q, (int)draft_idx) : 0.0f;
+                int32_t tok = -1, acc = 0;
+                float prob = 0.0f;
+                if (a.mode == kModeDistOnly) {
+                    tok = (int32_t)__shfl_sync(full, col, 0) + a.id_offset;
+                    prob = __fdiv_rn(__shfl_sync(full, q, 0), total);
+                } else {
+                    uint32_t skip_idx = 0xffffffffu;
+                    float walk_total = total;
+                    if (a.mode == kModeVerify) { // sampler.cpp:100-106
+                        acc = __fmul_rn(u_row, total) < q_draft;
+                        if (acc) {
+                            tok = draft;
+                            prob = __fdiv_rn(q_draft, total);
+                        } else {
+                            skip_idx = draft_idx;
+                            walk_total = __fsub_rn(total, q_draft);
+                            if (n == 1 && draft_idx == 0u) { // nothing but the rejected draft
+                                tok = draft;
+                                prob = 1.0f;
+                            }
+                        }
+                    }
+                    if (tok < 0) {
+                        float r = __fmul_rn((a.mode == kModeVerify) ? u2_row : u_row, walk_total);
+                        const float eps = 1e-6f * walk_total;
+                        const uint32_t first_valid = (skip_idx == 0u) ? 1u : 0u;
+                        const uint32_t last_valid = (skip_idx == n - 1u) ? n - 2u : n - 1u;
+                        const float qw = (lane == skip_idx) ? 0.0f : q; // the skipped draft never wins
+                        uint32_t hit = last_valid; // rounding: the last candidate (sampler.cpp:72)
+                        float q_hit = __shfl_sync(full, qw, (int)last_valid);
+                        bool found = false;
+                        for (uint32_t j = 0; j < n && !found; ++j) {
+                            const float qj = __shfl_sync(full, qw, (int)j);
+                            if (r < qj) {
+                                found = true;
+                                hit = j;
+                                q_hit = qj;
+                                // boundary below (not for the first candidate) or above (not for the last)
+                                if ((j != first_valid && r < eps) || (j < last_valid && __fsub_rn(qj, r) < eps))
+                                    fl |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                            } else {
+                                r = __fsub_rn(r, qj);
+                            }
+                        }
+                        tok = (int32_t)__shfl_sync(full, col, (int)hit) + a.id_offset;
+                        prob = __fdiv_rn(q_hit, walk_total);
+                    }
+                }
+                if (lane == 0) {
+                    if (a.token) a.token[row] = tok;
+                    if (a.prob) a.prob[row] = prob;
+                    if (a.flags) a.flags[row] = fl;
+                    if (a.n_cand) a.n_cand[row] = n;
+                    if (a.accepted) a.accepted[row] = acc;
+                    if (a.total_out) a.total_out[row] = total;
+                    if (a.timing)
+                        a.timing[(size_t)row * 64 + 3] = global_ns();
+                }
+                if (lane < min(n, a.cand_cap)) {
+                    if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + lane] = (int32_t)col + a.id_offset;
+                    if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + lane] = q;
+                }
+            }
+            if (lane == 0)
+                s.n_final = (n <= 32u) ? 1u : 0u; // 1: the row is done
+        }
+        __syncthreads();
+        if (s.n_final)
+            return;
+        __syncthreads(); // n_final is written again below
+        if (tid == 0)
+            s.n_final = 0;
+    }
 
     // need_sum: weight of the uncollected tail (the whole row for a shard record), relative to the row maximum:
     // sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
@@ -1472,8 +1667,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
 
     // exact weights of the collected elements, min_p filter (sampler.cpp:33-35)
-    if (a.timing && tid == 0)
-        a.timing[(size_t)row * 64 + 22] = global_ns();
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
     const uint32_t n_raw = min(s.ncand, a.scratch_cap);
     bool overflow = s.ncand > a.scratch_cap;
@@ -1511,8 +1704,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
         }
-        if (a.timing && tid == 0)
-            a.timing[(size_t)row * 64 + 23] = global_ns();
         if (cfg.need_sum) {
             // top_p's total (sampler.cpp:45-47) covers every column: exact weights for all that was collected, the
             // approximate sum for the rest. The margin that goes with it is 1e-5 of the approximate part plus the

@@ -55,6 +55,8 @@ struct RowKernelArgs {
     int pass;              // 0: first launch; 1: second pass, only the rows that asked for it (set by launch_row_kernel)
     int use_bulk_copy;     // 1: TMA bulk staging (aligned rows); 0: plain loads
     int overlap;           // MK_OVERLAP_*: launch behind the previous kernel of the stream programmatically
+    uint32_t debug_skip_tile;   // test hook: the copy of this tile is never requested (0xffffffff: none)
+    uint32_t debug_wait_probes; // test hook: probes a wait for a tile makes before it gives up (0: the default)
 };
 
 // Words of handle scratch per row: 4 per column of capacity, then 4 of per-row state (word 0: the row asks for the

@@ -236,3 +236,28 @@ def test_overlap_modes_give_the_same_tokens(gpu_sampler_factory, ref):
     for k in range(3):
         assert outs[k].cpu().tolist() == want[k], f"graph replay, launch {k}"
     s.set_overlap(0)
+
+
+@pytest.mark.parametrize("with_history", [True, False], ids=["fix-up warps wait", "readers wait"])
+def test_a_wait_that_runs_out_ends_the_row_in_good_order(ref, with_history):
+    """Every wait in the kernel is bounded. With the test hook that never requests one tile's copy, the waits for
+    that tile run out after a few milliseconds: each row returns token -1 with MK_FLAG_TIMEOUT, nothing traps or
+    hangs, and the same handle samples correctly right afterwards."""
+    import torch
+    from mako_b200 import BatchSampler, lib
+    v, b = 40003, 6
+    inp = Inputs(411, b, v, n_history=600 if with_history else 0)
+    p = SamplingParams(temperature=0.8, top_p=0.9, min_p=0.05, repetition_penalty=1.1, presence_penalty=0.5,
+                       frequency_penalty=0.3)
+    g = inp.to_gpu()
+    s = BatchSampler(v, b, 0)
+    assert lib.mk_debug_withhold_tile(s._h, 7, 100) == 0          # tile 7 of 10 never arrives; 100 probes of <= 20 us
+    res = s.sample(g["logits"], p, g["u"], **g["kw"])
+    torch.cuda.synchronize()
+    assert res.token.cpu().tolist() == [-1] * b
+    assert all(f == 0x40 for f in res.flags.cpu().tolist())
+    assert lib.mk_debug_withhold_tile(s._h, -1, 0) == 0
+    res = s.sample(g["logits"], p, g["u"], **g["kw"])
+    torch.cuda.synchronize()
+    want = [ref.sample(p, inp.logits[r], inp.u[r], **inp.row_kwargs(r))["token"] for r in range(b)]
+    assert res.token.cpu().tolist() == want
