@@ -167,6 +167,32 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
 int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                     int32_t* n_kept, int32_t* next_token, void* stream);
 
+/* One whole speculative round of the reference (src/gen/session.cpp:451-506) for rows->batch / n_pos sequences in
+ * one launch. rows->logits holds n_pos rows per sequence — row s*n_pos + j is the distribution after the round's
+ * token and drafts 0..j-1 (what Model::verify returns, src/gen/model.hpp:84-88) — while rows->history / history_len
+ * are per SEQUENCE (row s): the tokens accept()ed so far, the round's first token included. Position j < n_pos - 1
+ * verifies drafts[s][j] exactly as Sampler::verify would after the drafts before it were accepted: its penalties
+ * count history + drafts[s][0..j-1] (each kept draft is emit()ted before the next row is looked at, :491). The last
+ * position is the bonus row and is sampled (:505). forced[s][j] >= 0 (optional array) is the caller's forced token for
+ * that position: it takes the sampler's place without drawing, and a draft is kept only if it equals it (:481-484).
+ * u[s][0..n_pos] is the sequence's stream of uniforms in the order the reference's generator would produce them: a
+ * position takes the next one for its acceptance test (or its draw, for the bonus row) and the one after it for the
+ * redraw after a rejection; forced positions take none. Outputs: accepted / out->token per position as
+ * mk_sampler_verify_batch gives them, n_kept[s] = drafts kept up to the first rejection, next_token[s] = the
+ * replacement there, or the bonus row's token when every draft was kept — what Session::run carries into its next
+ * round. Positions after the first rejection are computed too and ignored, as positions of one launch must be. */
+int mk_sampler_spec_round(mk_sampler* s, const mk_rows* rows, uint32_t n_pos, const int32_t* drafts,
+                          const int32_t* forced, const float* u, const mk_sample_out* out, int32_t* accepted,
+                          int32_t* n_kept, int32_t* next_token, void* stream);
+
+/* The round's bookkeeping on the device: the kept drafts and then next_token[s] are appended to the sequence's
+ * history (the accept() calls of :420 for each emit(), the last one made at the top of the reference's next round),
+ * history_len[s] grows by n_kept[s] + 1, next_input[s] (optional) receives next_token[s]. A sequence whose round
+ * failed (next_token < 0) is left alone; a full history sets MK_FLAG_HISTORY_FULL in flags[s] (optional). */
+int mk_spec_commit(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* drafts, const int32_t* n_kept,
+                   const int32_t* next_token, int32_t* history, uint64_t history_ld, uint32_t history_cap,
+                   int32_t* history_len, int32_t* next_input, uint32_t* flags, void* stream);
+
 /* One step of the reference's drafter pick (ds_markov + ds_draft_pick, src/kernels/dsv41.metal:664-742; host loop
  * src/dsv41/engine.cpp:1474-1497) for up to 8 sequences that share the drafter: per sequence b,
  * score[v] = logits[b][v] + head[v] . embed[prev[b]] (head [n_vocab][rank], 16-byte aligned; embed [n_embed][rank]; rank a multiple of 4, <= 256),

@@ -104,6 +104,9 @@ def _load() -> C.CDLL:
     lib.mk_sampler_verify_batch.argtypes = [vp, C.POINTER(RowsC), vp, vp, vp, C.POINTER(SampleOutC), vp, vp]
     lib.mk_sampler_verify_pq_batch.argtypes = [vp, C.POINTER(RowsC), vp, C.c_uint64, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.mk_spec_resolve.argtypes = [vp, C.c_uint32, C.c_uint32, vp, vp, vp, vp, vp]
+    lib.mk_sampler_spec_round.argtypes = [vp, C.POINTER(RowsC), C.c_uint32, vp, vp, vp, C.POINTER(SampleOutC), vp, vp,
+                                          vp, vp]
+    lib.mk_spec_commit.argtypes = [vp, C.c_uint32, C.c_uint32, vp, vp, vp, vp, C.c_uint64, C.c_uint32, vp, vp, vp, vp]
     lib.mk_draft_pick.argtypes = [vp, vp, C.c_uint64, vp, vp, vp, C.c_uint64, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32,
                                   C.c_uint32, C.c_uint32, vp, vp, vp]
     lib.mk_draft_pick_plain.argtypes = [vp, vp, C.c_uint64, C.c_uint32, C.c_uint32, vp, C.c_uint64, vp, C.c_uint32,

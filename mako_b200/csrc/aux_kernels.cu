@@ -815,4 +815,45 @@ cudaError_t launch_decode_commit(uint32_t batch, const int32_t* sampled, const i
     return cudaGetLastError();
 }
 
+// ---- bookkeeping of one speculative round (src/gen/session.cpp:451-506) ----------------------------------------------
+// Per sequence: the drafts kept are accept()ed one by one as the reference emits them (:491), then the token that
+// follows them — the replacement at the first rejection, or the bonus row's token — which the reference emits at the
+// top of its next round (:456). The history grows by n_kept + 1 entries; next_input gets the token the engine runs
+// next.
+__global__ void spec_commit_kernel(uint32_t n_seq, uint32_t n_pos, const int32_t* drafts, const int32_t* n_kept,
+                                   const int32_t* next_token, int32_t* history, uint64_t history_ld,
+                                   uint32_t history_cap, int32_t* history_len, int32_t* next_input, uint32_t* flags)
+{
+    const uint32_t sq = blockIdx.x * blockDim.x + threadIdx.x;
+    if (sq >= n_seq)
+        return;
+    const int32_t kept = n_kept[sq], nxt = next_token[sq];
+    if (next_input)
+        next_input[sq] = nxt;
+    if (kept < 0 || nxt < 0) // a failed row (overflow, timeout): nothing is committed
+        return;
+    int32_t len = history_len[sq];
+    for (int32_t i = 0; i <= kept; ++i) {
+        const int32_t t = (i < kept) ? drafts[(size_t)sq * (n_pos - 1u) + (uint32_t)i] : nxt;
+        if (len >= 0 && (uint32_t)len < history_cap) {
+            history[(size_t)sq * history_ld + (uint32_t)len] = t; // Sampler::accept (sampler.cpp:15-18)
+            ++len;
+        } else if (flags) {
+            flags[sq] |= MK_FLAG_HISTORY_FULL;
+        }
+    }
+    history_len[sq] = len;
+}
+
+cudaError_t launch_spec_commit(uint32_t n_seq, uint32_t n_pos, const int32_t* drafts, const int32_t* n_kept,
+                               const int32_t* next_token, int32_t* history, uint64_t history_ld, uint32_t history_cap,
+                               int32_t* history_len, int32_t* next_input, uint32_t* flags, cudaStream_t stream)
+{
+    if (n_seq == 0)
+        return cudaSuccess;
+    spec_commit_kernel<<<(n_seq + 127) / 128, 128, 0, stream>>>(n_seq, n_pos, drafts, n_kept, next_token, history,
+                                                                 history_ld, history_cap, history_len, next_input, flags);
+    return cudaGetLastError();
+}
+
 } // namespace mk

@@ -485,6 +485,51 @@ int mk_spec_resolve(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t
     return MK_OK;
 }
 
+int mk_sampler_spec_round(mk_sampler* s, const mk_rows* rows, uint32_t n_pos, const int32_t* drafts,
+                          const int32_t* forced, const float* u, const mk_sample_out* out, int32_t* accepted,
+                          int32_t* n_kept, int32_t* next_token, void* stream)
+{
+    if (int rc = check_rows(s, rows))
+        return rc;
+    if (n_pos == 0 || rows->batch % n_pos != 0)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_sampler_spec_round: batch %u is not a multiple of n_pos %u",
+                    rows->batch, n_pos);
+    if (!out || !out->token || !accepted || !n_kept || !next_token || (n_pos > 1 && !drafts))
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_sampler_spec_round: drafts, accepted, n_kept, next_token and "
+                                             "out->token are required");
+    if (!u && !all_greedy(rows))
+        return fail(MK_ERR_INVALID_ARGUMENT, "uniforms are required unless every row is greedy");
+    DeviceGuard g(s->device);
+    mk::RowKernelArgs a;
+    fill_common(a, s, rows);
+    fill_out(a, out);
+    a.u = u;
+    a.accepted = accepted;
+    a.mode = mk::kModeVerify; // per row: the last position of a sequence is sampled, the others are verified
+    a.spec_n_pos = n_pos;
+    a.spec_drafts = drafts;
+    a.spec_forced = forced;
+    MK_CUDA(mk::launch_row_kernel(a, rows->batch, (cudaStream_t)stream));
+    MK_CUDA(mk::launch_spec_resolve(rows->batch / n_pos, n_pos, accepted, out->token, n_kept, next_token,
+                                    (cudaStream_t)stream));
+    return MK_OK;
+}
+
+int mk_spec_commit(mk_sampler* s, uint32_t n_seq, uint32_t n_pos, const int32_t* drafts, const int32_t* n_kept,
+                   const int32_t* next_token, int32_t* history, uint64_t history_ld, uint32_t history_cap,
+                   int32_t* history_len, int32_t* next_input, uint32_t* flags, void* stream)
+{
+    if (!s || !n_kept || !next_token || !history || !history_len || n_pos == 0 || (n_pos > 1 && !drafts))
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_spec_commit: null argument or n_pos == 0");
+    if (history_ld < history_cap || history_cap > 65535u)
+        return fail(MK_ERR_INVALID_ARGUMENT, "mk_spec_commit: history_ld %llu, history_cap %u (at most 65535)",
+                    (unsigned long long)history_ld, history_cap);
+    DeviceGuard g(s->device);
+    MK_CUDA(mk::launch_spec_commit(n_seq, n_pos, drafts, n_kept, next_token, history, history_ld, history_cap,
+                                   history_len, next_input, flags, (cudaStream_t)stream));
+    return MK_OK;
+}
+
 uint32_t mk_vp_record_bytes(uint32_t k)
 {
     return mk::vp_record_bytes(k);

@@ -751,6 +751,16 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const uint32_t V = a.n_vocab;
     const uint32_t n_tiles = (V + kTile - 1) / kTile;
     const float* __restrict__ lrow = a.logits + (size_t)row * a.ld;
+    // A speculative round (src/gen/session.cpp:451-506): row = sequence * n_pos + position. Position j < n_pos - 1
+    // verifies draft j, the last one is the bonus row and is sampled; the penalties of position j count the sequence's
+    // history plus drafts 0..j-1 (each accepted draft is emit()ted before the next row is looked at, :491); a forced
+    // token takes the place of the sampler and draws nothing (:481-484), so the position's uniforms are found by
+    // counting the positions before it that are not forced.
+    const bool spec = a.spec_n_pos != 0u;
+    const uint32_t seq = spec ? row / a.spec_n_pos : row, pos = spec ? row - seq * a.spec_n_pos : 0u;
+    const int mode = spec ? ((pos + 1u == a.spec_n_pos) ? (int)kModeSample : (int)kModeVerify) : a.mode;
+    const int32_t* __restrict__ extra = spec ? a.spec_drafts + (size_t)seq * (a.spec_n_pos - 1u) : nullptr;
+    const uint32_t n_extra = spec ? pos : 0u;
     // Launched programmatically behind the previous kernel of the stream, this grid may start while that one still
     // runs. Nothing that kernel may have written is touched before griddep_wait() — which comes first thing, unless
     // the caller has declared the side inputs (parameters, histories, biases) stable: then the whole set-up runs
@@ -768,13 +778,15 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // A per-row length read from device memory is clamped to what the row's buffer holds and to the 16-bit counters
     // of the long-history path; a clamp that bites is reported in the row's flags (MK_FLAG_HISTORY_FULL).
     const uint32_t hlen_cap = (uint32_t)min((uint64_t)65535u, a.history_ld);
-    const uint32_t hlen_dev = (a.history && a.history_len) ? (uint32_t)max(a.history_len[row], 0) : 0u;
+    const uint32_t hlen_dev = (a.history && a.history_len) ? (uint32_t)max(a.history_len[seq], 0) : 0u;
     const bool hlen_clamped = hlen_dev > hlen_cap;
-    const uint32_t hlen_all = a.history ? (a.history_len ? min(hlen_dev, hlen_cap) : a.n_history) : 0u;
+    const uint32_t hlen_base = a.history ? (a.history_len ? min(hlen_dev, hlen_cap) : a.n_history) : 0u;
+    const uint32_t hlen_all = hlen_base + n_extra;
     const bool has_hist = !(prm.temperature <= 0.0f) && hlen_all > 0 &&
                           !(prm.repetition_penalty == 1.0f && prm.presence_penalty == 0.0f && prm.frequency_penalty == 0.0f);
     const uint32_t hlen = has_hist ? hlen_all : 0u;
-    const int32_t* __restrict__ hrow = a.history ? a.history + (size_t)row * a.history_ld : nullptr;
+    const int32_t* __restrict__ hrow = a.history ? a.history + (size_t)seq * a.history_ld : nullptr;
+    auto hist_at = [&](uint32_t j) -> int32_t { return j < hlen_base ? __ldg(hrow + j) : __ldg(extra + (j - hlen_base)); };
     const uint32_t nb = a.bias ? a.n_bias : 0u;
     const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
     // Columns whose value is not the one in memory — generated tokens (penalties) and biased tokens — are "special":
@@ -793,10 +805,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 #pragma unroll
         for (int i = 0; i < kHistPerThread; ++i) {
             const uint32_t j = (uint32_t)i * kThreads + tid;
-            hc[i] = (j < hlen) ? (uint32_t)__ldg(hrow + j) - (uint32_t)a.id_offset : 0xffffffffu;
+            hc[i] = (j < hlen) ? (uint32_t)hist_at(j) - (uint32_t)a.id_offset : 0xffffffffu;
         }
     }
-    const RowCfg cfg = make_cfg(prm, V, a.mode, a.vp_k, a.pass);
+    const RowCfg cfg = make_cfg(prm, V, mode, a.vp_k, a.pass);
     const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
     // Per-row scratch, 16 bytes per column: scratch_cap raw candidates (logit bits, column) — sorted in place as
     // 64-bit keys by the large sorted-list path — then as much again: the merge sort's second buffer, or (large
@@ -805,6 +817,21 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     uint2* __restrict__ scratch = reinterpret_cast<uint2*>(row_scratch);
     float* __restrict__ qrow = reinterpret_cast<float*>(row_scratch + 2u * a.scratch_cap);
     uint32_t* const again = row_scratch + 4u * a.scratch_cap; // set by the first launch: this row wants the second pass
+    if (spec && a.spec_forced) {
+        const int32_t f = __ldg(a.spec_forced + row);
+        if (f >= 0) { // the sampler is bypassed: the token is the forced one, a draft is kept only if it matches
+            if (early)
+                griddep_wait();
+            if (tid == 0 && a.pass == 0) {
+                if (a.token) a.token[row] = f;
+                if (a.prob) a.prob[row] = 1.0f;
+                if (a.flags) a.flags[row] = 0u;
+                if (a.n_cand) a.n_cand[row] = 0u;
+                if (a.accepted) a.accepted[row] = (mode == kModeVerify && f == __ldg(extra + pos)) ? 1 : 0;
+            }
+            return;
+        }
+    }
     if (a.pass == 1 && again[0] == 0u)
         return;
     // ---- shared-memory layout of the streaming phase ---------------------------------------------------------------
@@ -978,9 +1005,18 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     griddep_launch_dependents();
     if (a.pass == 0 && tid == 0)
         again[0] = 0u;
-    const float u_row = a.u ? __ldg(a.u + row) : 0.0f;
-    const float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
-    const int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
+    float u_row = a.u ? __ldg(a.u + (spec ? 0u : row)) : 0.0f;
+    float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
+    int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
+    if (spec) {
+        uint32_t drawn = 0; // uniforms the positions before this one consume when every draft before it is kept
+        for (uint32_t i = 0; i < pos; ++i)
+            drawn += (a.spec_forced && __ldg(a.spec_forced + (size_t)seq * a.spec_n_pos + i) >= 0) ? 0u : 1u;
+        const float* useq = a.u + (size_t)seq * (a.spec_n_pos + 1u);
+        u_row = __ldg(useq + drawn);
+        u2_row = __ldg(useq + drawn + 1u);
+        draft_row = (mode == kModeVerify) ? __ldg(extra + pos) : -1;
+    }
     if (prefixed > 0) {
         // requested before the set-up, the first tiles have landed by now (requested after the wait, they are
         // waited for here)
@@ -1126,13 +1162,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     // count the tile's ids in 16-bit counters, then the first lane to clear a counter owns that id
                     // and applies the penalties with its count
                     for (uint32_t j = lane; j < hlen; j += 32) {
-                        const int64_t loc = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
+                        const int64_t loc = (int64_t)hist_at(j) - a.id_offset - (int64_t)base;
                         if (loc >= 0 && loc < (int64_t)n_t)
                             atomicAdd(&cnt[(uint32_t)loc >> 1], 1u << (((uint32_t)loc & 1u) * 16u));
                     }
                     __syncwarp();
                     for (uint32_t j = lane; j < hlen; j += 32) {
-                        const int64_t loc64 = (int64_t)hrow[j] - a.id_offset - (int64_t)base;
+                        const int64_t loc64 = (int64_t)hist_at(j) - a.id_offset - (int64_t)base;
                         if (loc64 >= 0 && loc64 < (int64_t)n_t) {
                             const uint32_t loc = (uint32_t)loc64, sh = (loc & 1u) * 16u;
                             const uint32_t old = atomicAnd(&cnt[loc >> 1], ~(0xffffu << sh));
@@ -1154,8 +1190,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         uint64_t* const avail = has_special ? s.ready : s.full;
         const float c2 = cfg.inv_t * 1.4426950408889634f;
         const float ninf = -__int_as_float(0x7f800000);
-        const bool collect = !cfg.greedy || a.mode == kModeVpLocal;
-        const bool sum_all = a.mode == kModeVpLocal;
+        const bool collect = !cfg.greedy || mode == kModeVpLocal;
+        const bool sum_all = mode == kModeVpLocal;
         float warp_pub = ninf;
         // The loop over the tiles is compiled four times, with the mask, the top_k histogram and the streamed sum
         // compiled in or out: a row runs a variant that holds little beyond its own work. (One loop with all
@@ -1406,7 +1442,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // is short and contiguous; every other row falls through to the general finish below, which recomputes from the
     // collected elements.
     constexpr uint32_t kFastRaw = 256;
-    if (a.mode != kModeVpLocal && !cfg.greedy && !cfg.need_sum && !s.nan0 && s.ncand <= kFastRaw &&
+    if (mode != kModeVpLocal && !cfg.greedy && !cfg.need_sum && !s.nan0 && s.ncand <= kFastRaw &&
         s.ncand <= a.scratch_cap) {
         if (warp == 0) {
             const uint32_t full = 0xffffffffu;
@@ -1499,19 +1535,19 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 float total = 0.0f;
                 for (uint32_t j = 0; j < n; ++j)
                     total = __fadd_rn(total, __shfl_sync(full, q, (int)j));
-                const int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
+                const int32_t draft = (mode == kModeVerify) ? draft_row : -1;
                 const uint32_t dm = __ballot_sync(full, draft >= 0 && lane < n && (int32_t)col + a.id_offset == draft);
                 const uint32_t draft_idx = dm ? (uint32_t)__ffs((int)dm) - 1u : 0xffffffffu;
                 const float q_draft = dm ? __shfl_sync(full, q, (int)draft_idx) : 0.0f;
                 int32_t tok = -1, acc = 0;
                 float prob = 0.0f;
-                if (a.mode == kModeDistOnly) {
+                if (mode == kModeDistOnly) {
                     tok = (int32_t)__shfl_sync(full, col, 0) + a.id_offset;
                     prob = __fdiv_rn(__shfl_sync(full, q, 0), total);
                 } else {
                     uint32_t skip_idx = 0xffffffffu;
                     float walk_total = total;
-                    if (a.mode == kModeVerify) { // sampler.cpp:100-106
+                    if (mode == kModeVerify) { // sampler.cpp:100-106
                         acc = __fmul_rn(u_row, total) < q_draft;
                         if (acc) {
                             tok = draft;
@@ -1526,7 +1562,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         }
                     }
                     if (tok < 0) {
-                        float r = __fmul_rn((a.mode == kModeVerify) ? u2_row : u_row, walk_total);
+                        float r = __fmul_rn((mode == kModeVerify) ? u2_row : u_row, walk_total);
                         const float eps = 1e-6f * walk_total;
                         const uint32_t first_valid = (skip_idx == 0u) ? 1u : 0u;
                         const uint32_t last_valid = (skip_idx == n - 1u) ? n - 2u : n - 1u;
@@ -1604,7 +1640,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         __syncthreads(); // warp_sum is written again below
     }
 
-    if (a.mode == kModeVpLocal) {
+    if (mode == kModeVpLocal) {
         // Shard record: header {max, n, sum} then the k best (logit, global id), by (logit desc, id asc).
         unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
         const uint32_t n_all = min(s.ncand, a.scratch_cap);
@@ -1660,7 +1696,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             if (a.cand_ids && a.cand_cap) a.cand_ids[(size_t)row * a.cand_cap] = t;
             if (a.cand_q && a.cand_cap) a.cand_q[(size_t)row * a.cand_cap] = 1.0f;
             if (a.total_out) a.total_out[row] = 1.0f;
-            if (a.mode == kModeVerify && a.accepted)
+            if (mode == kModeVerify && a.accepted)
                 a.accepted[row] = (draft_row == t) ? 1 : 0;
         }
         return;
@@ -1731,7 +1767,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     if (!overflow && n > (uint32_t)kSortCap && !cfg.use_topp && !(cfg.top_k > 0 && cfg.top_k < n)) {
         const RowOut o = {a.token, a.prob, a.flags, a.n_cand, a.accepted, a.total_out, a.cand_ids, a.cand_q,
-                          a.cand_cap, a.id_offset, a.timing, a.mode};
+                          a.cand_cap, a.id_offset, a.timing, mode};
         wide_id_ordered(s, reinterpret_cast<float*>(dyn + kOffKeys), scratch, qrow, n_raw, n, V,
                         fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key)), m, cfg.inv_t, cfg.minp_eff, row,
                         flags, u_row, u2_row, draft_row, o);
@@ -1739,7 +1775,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     const unsigned long long* ksrc = keys; // the ordered list: shared memory, or the row's scratch for a long one
     bool pre_sorted = false;
-    if (!overflow && n > (uint32_t)kSortCap && a.mode != kModeDistOnly) {
+    if (!overflow && n > (uint32_t)kSortCap && mode != kModeDistOnly) {
         // More candidates than the shared-memory sort holds, and a truncation that orders them (the unordered case
         // returned above): a flat row under top_p, or a very large top_k. The candidates are sorted in global
         // memory — 8192-key runs in shared memory, then merge passes between the two halves of the row's scratch —
@@ -1872,7 +1908,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // the same sequential chain, so the chain never waits for memory.
     if (warp == 0) {
         const uint32_t full = 0xffffffffu;
-        const int32_t draft = (a.mode == kModeVerify) ? draft_row : -1;
+        const int32_t draft = (mode == kModeVerify) ? draft_row : -1;
         if (cfg.use_topp && short_list) { // sampler.cpp:44-61, sequentially
             double total_d = 0.0, band;
             if (cfg.need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
@@ -1940,7 +1976,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
         int32_t tok = -1, acc = 0;
         float prob = 0.0f;
-        if (a.mode == kModeDistOnly) {
+        if (mode == kModeDistOnly) {
             float q0;
             uint32_t c0;
             fetch(0, q0, c0);
@@ -1949,7 +1985,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         } else {
             uint32_t skip_idx = 0xffffffffu;
             float walk_total = total;
-            if (a.mode == kModeVerify) { // sampler.cpp:100-106
+            if (mode == kModeVerify) { // sampler.cpp:100-106
                 acc = __fmul_rn(u_row, total) < q_draft;
                 if (acc) {
                     tok = draft;
@@ -1964,7 +2000,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
             if (tok < 0) {
-                float r = __fmul_rn((a.mode == kModeVerify) ? u2_row : u_row, walk_total);
+                float r = __fmul_rn((mode == kModeVerify) ? u2_row : u_row, walk_total);
                 const float eps = 1e-6f * walk_total;
                 const uint32_t first_valid = (skip_idx == 0u) ? 1u : 0u;
                 const uint32_t last_valid = (skip_idx == n - 1u) ? n - 2u : n - 1u;

@@ -55,6 +55,10 @@ struct RowKernelArgs {
     int pass;              // 0: first launch; 1: second pass, only the rows that asked for it (set by launch_row_kernel)
     int use_bulk_copy;     // 1: TMA bulk staging (aligned rows); 0: plain loads
     int overlap;           // MK_OVERLAP_*: launch behind the previous kernel of the stream programmatically
+    // a speculative round: row = sequence * spec_n_pos + position (0: off); history and history_len are per sequence
+    uint32_t spec_n_pos;
+    const int32_t* spec_drafts; // [n_seq][spec_n_pos - 1]
+    const int32_t* spec_forced; // [n_seq][spec_n_pos] forced token or -1, or NULL
     uint32_t debug_skip_tile;   // test hook: the copy of this tile is never requested (0xffffffff: none)
     uint32_t debug_wait_probes; // test hook: probes a wait for a tile makes before it gives up (0: the default)
 };
@@ -96,6 +100,10 @@ cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream);
 
 cudaError_t launch_spec_resolve(uint32_t n_seq, uint32_t n_pos, const int32_t* accepted, const int32_t* token,
                                 int32_t* n_kept, int32_t* next_token, cudaStream_t stream);
+
+cudaError_t launch_spec_commit(uint32_t n_seq, uint32_t n_pos, const int32_t* drafts, const int32_t* n_kept,
+                               const int32_t* next_token, int32_t* history, uint64_t history_ld, uint32_t history_cap,
+                               int32_t* history_len, int32_t* next_input, uint32_t* flags, cudaStream_t stream);
 
 constexpr uint32_t kDraftPickMaxSeq = 8, kDraftPickMaxRank = 256;
 cudaError_t launch_draft_pick(const float* logits, uint64_t ld, const float* head, const float* embed, const float* x,

@@ -273,6 +273,36 @@ class BatchSampler:
                                   nxt.data_ptr(), _stream_ptr(self.device)))
         return kept, nxt
 
+    def spec_round(self, logits, params, drafts, u, *, history=None, history_len=None, forced=None, mask=None,
+                   bias=None):
+        """One speculative round of the reference (src/gen/session.cpp:451-506) for every sequence in one launch.
+        logits [n_seq * n_pos, V]: row s*n_pos + j follows the round's token and drafts 0..j-1; drafts [n_seq,
+        n_pos - 1] int32; u [n_seq, n_pos + 1] the sequence's uniforms in generator order; history [n_seq, cap] and
+        history_len [n_seq] per sequence; forced [n_seq, n_pos] int32 (token or -1) or None. Returns (n_kept [n_seq],
+        next_token [n_seq], result with per-position token / accepted / flags)."""
+        n_seq, n_drafts = drafts.shape
+        n_pos = n_drafts + 1
+        assert logits.shape[0] == n_seq * n_pos and drafts.dtype == torch.int32 and drafts.is_contiguous()
+        assert u.shape == (n_seq, n_pos + 1) and u.dtype == torch.float32 and u.is_contiguous()
+        if forced is not None:
+            assert forced.shape == (n_seq, n_pos) and forced.dtype == torch.int32 and forced.is_contiguous()
+        r = self._rows(logits, params, history, history_len, mask, bias)
+        o = self._out(r.batch)
+        kept = torch.empty(n_seq, dtype=torch.int32, device=self.device)
+        nxt = torch.empty(n_seq, dtype=torch.int32, device=self.device)
+        check(lib.mk_sampler_spec_round(self._h, C.byref(r), n_pos, drafts.data_ptr(), _ptr(forced), u.data_ptr(),
+                                        C.byref(o), self.accepted.data_ptr(), kept.data_ptr(), nxt.data_ptr(),
+                                        _stream_ptr(self.device)))
+        return kept, nxt, self._result(r.batch, accepted=self.accepted[: r.batch])
+
+    def spec_commit(self, drafts, n_kept, next_token, history, history_len, *, next_input=None, flags=None) -> None:
+        """The round's bookkeeping on the device: kept drafts, then next_token, appended to each sequence's history
+        (history [n_seq, cap] and history_len [n_seq] updated in place); next_input receives next_token."""
+        n_seq, n_drafts = drafts.shape
+        check(lib.mk_spec_commit(self._h, n_seq, n_drafts + 1, drafts.data_ptr(), n_kept.data_ptr(),
+                                 next_token.data_ptr(), history.data_ptr(), history.stride(0), history.shape[1],
+                                 history_len.data_ptr(), _ptr(next_input), _ptr(flags), _stream_ptr(self.device)))
+
     def vp_local(self, shard_logits, params, k: int, records: torch.Tensor, *, id_offset: int, history=None,
                  history_len=None, mask=None, bias=None) -> torch.Tensor:
         """Vocab-parallel step 1: this shard's per-row record (max, sum-exp, k best) into `records` (uint8)."""
