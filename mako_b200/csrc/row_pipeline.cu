@@ -63,7 +63,6 @@ constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates
 #define MK_PREFIX_TILES 4
 #endif
 constexpr int kPrefixTiles = MK_PREFIX_TILES;  // tiles all warps edit before the stream starts (their columns fit 16 bits)
-constexpr uint32_t kNoBias = 0x7fa00001u; // a NaN payload no caller's bias carries: this rank has no bias
 constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
 constexpr int kBinShift = 21;
 
@@ -234,9 +233,8 @@ __device__ __forceinline__ uint32_t nth_set_bit(uint32_t w, uint32_t n)
 // binary search over the per-word ranks and a find-n-th-set-bit in the word, and indexes the count directly. Every
 // column is touched by exactly one thread. `tile` points at column `col0` of the row in shared memory.
 __device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t* wpre, const uint32_t* counts,
-                                         const uint32_t* biasval, float* tile, uint32_t col0, uint32_t w_lo,
-                                         uint32_t w_hi, uint32_t r_lo, uint32_t r_hi, uint32_t thr, uint32_t n_thr,
-                                         const RowCfg& cfg)
+                                         float* tile, uint32_t col0, uint32_t w_lo, uint32_t w_hi, uint32_t r_lo,
+                                         uint32_t r_hi, uint32_t thr, uint32_t n_thr, const RowCfg& cfg)
 {
     for (uint32_t r = r_lo + thr; r < r_hi; r += n_thr) {
         uint32_t lo = w_lo, hi = w_hi; // largest word in [lo, hi) whose rank is <= r
@@ -250,13 +248,7 @@ __device__ __forceinline__ void fix_hits(const uint32_t* bitmap, const uint16_t*
         const uint32_t bit = nth_set_bit(bitmap[lo], r - (uint32_t)wpre[lo]);
         const uint32_t n = (counts[r >> 1] >> ((r & 1u) * 16u)) & 0xffffu;
         const uint32_t loc = (lo << 5) + bit - col0;
-        float v = tile[loc];
-        if (biasval) {
-            const uint32_t bv = biasval[r];
-            if (bv != kNoBias)
-                v = __fadd_rn(v, __uint_as_float(bv));
-        }
-        tile[loc] = n ? penalise(v, n, cfg) : v;
+        tile[loc] = penalise(tile[loc], n, cfg);
     }
 }
 
@@ -740,6 +732,9 @@ __device__ __noinline__ const unsigned long long* long_sort(Smem& s, unsigned lo
 
 } // namespace
 
+// kSpec: the rows of a speculative round (row = sequence * n_pos + position); compiled apart, so that the plain
+// kernel carries none of its bookkeeping.
+template <bool kSpec>
 __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKernelArgs a)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -756,7 +751,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // history plus drafts 0..j-1 (each accepted draft is emit()ted before the next row is looked at, :491); a forced
     // token takes the place of the sampler and draws nothing (:481-484), so the position's uniforms are found by
     // counting the positions before it that are not forced.
-    const bool spec = a.spec_n_pos != 0u;
+    constexpr bool spec = kSpec;
     const uint32_t seq = spec ? row / a.spec_n_pos : row, pos = spec ? row - seq * a.spec_n_pos : 0u;
     const int mode = spec ? ((pos + 1u == a.spec_n_pos) ? (int)kModeSample : (int)kModeVerify) : a.mode;
     const int32_t* __restrict__ extra = spec ? a.spec_drafts + (size_t)seq * (a.spec_n_pos - 1u) : nullptr;
@@ -786,17 +781,22 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                           !(prm.repetition_penalty == 1.0f && prm.presence_penalty == 0.0f && prm.frequency_penalty == 0.0f);
     const uint32_t hlen = has_hist ? hlen_all : 0u;
     const int32_t* __restrict__ hrow = a.history ? a.history + (size_t)seq * a.history_ld : nullptr;
-    auto hist_at = [&](uint32_t j) -> int32_t { return j < hlen_base ? __ldg(hrow + j) : __ldg(extra + (j - hlen_base)); };
+    auto hist_at = [&](uint32_t j) -> int32_t {
+        if constexpr (kSpec)
+            return j < hlen_base ? __ldg(hrow + j) : __ldg(extra + (j - hlen_base));
+        else
+            return __ldg(hrow + j);
+    };
     const uint32_t nb = a.bias ? a.n_bias : 0u;
     const mk_bias* __restrict__ brow = a.bias ? a.bias + (size_t)row * a.n_bias : nullptr;
-    // Columns whose value is not the one in memory — generated tokens (penalties) and biased tokens — are "special":
-    // two fix-up warps edit them in every tile in shared memory before the readers see it. While they are few (the
-    // usual case) a bitmap names them, with rank-indexed tables of counts and biases behind it, and a fix-up lane
-    // walks the set bits of its 128 columns; a longer history, or a vocabulary beyond the bitmap, takes the slower
-    // path where one warp matches the whole history against every tile.
+    // Columns whose value is not the one in memory — biased tokens and generated tokens (penalties) — are edited by
+    // two fix-up warps in every tile in shared memory before the readers see it. While the history is short (the
+    // usual case) a bitmap names the generated columns, with rank-indexed counts behind it, and a tile's columns are
+    // spread over the lanes by rank; a longer history, or a vocabulary beyond the bitmap, takes the slower path where
+    // one warp matches the whole history against every tile. The few bias entries are matched against each tile.
     const bool has_special = has_hist || nb > 0;
-    const bool use_table = has_special && hlen + nb <= (uint32_t)kHistCap && V <= kMaxBitmapVocab;
-    const bool tile_fix = has_special && !use_table;
+    const bool use_table = has_hist && hlen <= (uint32_t)kHistCap && V <= kMaxBitmapVocab;
+    const bool long_history = has_hist && !use_table;
     // The history is read into registers first thing, all loads in flight together, so that their latency
     // overlaps the barrier set-up instead of being paid once per loop trip.
     constexpr int kHistPerThread = (kHistCap + kThreads - 1) / kThreads;
@@ -835,18 +835,15 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (a.pass == 1 && again[0] == 0u)
         return;
     // ---- shared-memory layout of the streaming phase ---------------------------------------------------------------
-    const bool use_bias = use_table && nb > 0;
     const uint32_t bm_words = (V + 31u) / 32u;
     unsigned char* const dyn = smem_raw + kHeadBytes;
     uint32_t off = 0;
-    uint32_t* const bitmap = reinterpret_cast<uint32_t*>(dyn + off); // tile_fix: per-tile id counters instead
-    off += use_table ? ((bm_words * 4u + 15u) & ~15u) : (tile_fix ? (uint32_t)kTile * 2u : 0u);
+    uint32_t* const bitmap = reinterpret_cast<uint32_t*>(dyn + off); // long histories: per-tile id counters instead
+    off += use_table ? ((bm_words * 4u + 15u) & ~15u) : (long_history ? (uint32_t)kTile * 2u : 0u);
     uint16_t* const wpre = reinterpret_cast<uint16_t*>(dyn + off); // rank of each bitmap word's first set bit
     off += use_table ? ((bm_words * 2u + 15u) & ~15u) : 0u;
     uint32_t* const counts = reinterpret_cast<uint32_t*>(dyn + off); // by rank: occurrences, two per word
     off += use_table ? (uint32_t)kHistCap * 2u : 0u;
-    uint32_t* const biasval = reinterpret_cast<uint32_t*>(dyn + off); // by rank: bias as float bits, or kNoBias
-    off += use_bias ? (uint32_t)kHistCap * 4u : 0u;
     uint32_t* const hist = reinterpret_cast<uint32_t*>(dyn + off);
     off += cfg.hist_mode ? (uint32_t)kBins * 4u : 0u;
     off = (off + 127u) & ~127u;
@@ -876,8 +873,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         s.n_own = 0;
         fence_barrier_init();
     }
-    uint32_t* const cnt = bitmap; // tile_fix: per-tile id counters (two 16-bit counters per word)
-    if (tile_fix)
+    uint32_t* const cnt = bitmap; // long histories: per-tile id counters (two 16-bit counters per word)
+    if (long_history)
         for (uint32_t i = tid; i < kTile / 2; i += kThreads)
             cnt[i] = 0;
     if (cfg.hist_mode)
@@ -889,9 +886,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                                        reinterpret_cast<unsigned char*>(bitmap)) / 16u;
         for (uint32_t i = tid; i < nz; i += kThreads)
             z[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (use_bias)
-            for (uint32_t i = tid; i < (uint32_t)kHistCap; i += kThreads)
-                biasval[i] = kNoBias;
     }
     __syncthreads();
     if (a.timing && tid == 0 && !early)
@@ -950,12 +944,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     own_list[at] = (uint16_t)hc[hi];
             }
         }
-        for (uint32_t j = tid; j < nb; j += kThreads) {
-            const int32_t id = brow[j].id;
-            const int64_t loc = (int64_t)id - a.id_offset;
-            if (id >= 0 && loc >= 0 && loc < (int64_t)V)
-                atomicOr(&bitmap[(uint32_t)loc >> 5], 1u << ((uint32_t)loc & 31u));
-        }
         __syncthreads();
         if (a.timing && tid == 0 && !early)
             a.timing[(size_t)row * 64 + 7] = global_ns();
@@ -980,15 +968,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 if (hc[hi] < V)
                     atomicAdd(&counts[rk[hi] >> 1], 1u << ((rk[hi] & 1u) * 16u));
         }
-        for (uint32_t j = tid; j < nb; j += kThreads) {
-            const mk_bias be = brow[j];
-            const int64_t loc = (int64_t)be.id - a.id_offset;
-            if (be.id >= 0 && loc >= 0 && loc < (int64_t)V) {
-                const uint32_t col = (uint32_t)loc;
-                biasval[wpre[col >> 5] + __popc(bitmap[col >> 5] & ((1u << (col & 31u)) - 1u))] =
-                    __float_as_uint(be.value);
-            }
-        }
         __syncthreads();
         if (a.timing && tid == 0 && !early)
             a.timing[(size_t)row * 64 + 4] = global_ns();
@@ -1008,7 +987,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     float u_row = a.u ? __ldg(a.u + (spec ? 0u : row)) : 0.0f;
     float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
     int32_t draft_row = a.draft ? __ldg(a.draft + row) : -1;
-    if (spec) {
+    if constexpr (kSpec) {
         uint32_t drawn = 0; // uniforms the positions before this one consume when every draft before it is kept
         for (uint32_t i = 0; i < pos; ++i)
             drawn += (a.spec_forced && __ldg(a.spec_forced + (size_t)seq * a.spec_n_pos + i) >= 0) ? 0u : 1u;
@@ -1107,41 +1086,23 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             }
         }
     } else if (warp <= kFixers / 32) {
-        if (use_table) {
-            // fix-up warps: each owns every other tile of those that follow the ones edited above. The tile's generated
-            // columns are spread evenly over the lanes by rank: a rank is turned back into its column by a binary
-            // search over the per-word ranks and a find-n-th-set-bit, and indexes count and bias directly; the edit is
-            // bias, then the penalties (sampler.cpp:23-28). Nothing synchronises across the two warps.
+        // fix-up: each of the two warps owns every other tile of those that follow the ones edited above (a long
+        // history: warp 0 owns them all, because its per-tile counters are shared), so two tiles are edited at a time
+        // and nothing synchronises across warps
+        if (has_special) {
             const uint32_t fw = warp - 1;
-            constexpr uint32_t kFixWarps = kFixers / 32;
             if (fw == 0 && lane == 0)
                 for (uint32_t t = 0; t < prefixed; ++t) // edited by all warps above
                     mbar_arrive(&s.ready[t]);
-            const uint32_t t_first = prefixed + (fw + kFixWarps - (prefixed % kFixWarps)) % kFixWarps; // t % 2 == fw
+            const uint32_t t_step = long_history ? 1u : (uint32_t)(kFixers / 32);
+            uint32_t t_first = prefixed;
+            if (!long_history)
+                t_first += (fw + (kFixers / 32) - (prefixed % (kFixers / 32))) % (kFixers / 32); // t % 2 == fw
+            const bool idle = long_history && fw != 0;
             uint32_t st = t_first % n_stages, k = t_first / n_stages;
-            for (uint32_t t = t_first; t < n_tiles; t += kFixWarps, st += kFixWarps) {
+            for (uint32_t t = t_first; t < n_tiles && !idle; t += t_step, st += t_step) {
                 if (st >= n_stages) {
                     st -= n_stages;
-                    ++k;
-                }
-                const uint32_t base = t * kTile, n_t = min((uint32_t)kTile, V - base);
-                const uint32_t w_lo = base >> 5, w_hi = min((base + n_t + 31u) >> 5, bm_words);
-                const uint32_t r_lo = (uint32_t)wpre[w_lo], r_hi = (w_hi < bm_words) ? (uint32_t)wpre[w_hi] : s.n_distinct;
-                if (!mbar_wait(&s.full[st], k & 1, (*(volatile uint32_t*)&s.abort_flag) ? 1u : wait_probes))
-                    atomicExch(&s.abort_flag, 1u);
-                fix_hits(bitmap, wpre, counts, use_bias ? biasval : nullptr, ring + st * kTile, base, w_lo, w_hi, r_lo,
-                         r_hi, lane, 32u, cfg);
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(&s.ready[st]);
-            }
-        } else if (tile_fix && warp == 1) {
-            // fix-up warp of the slow path: edits every tile in shared memory before the readers see it — bias, then
-            // the penalties of the tile's generated columns.
-            uint32_t st = 0, k = 0;
-            for (uint32_t t = 0; t < n_tiles; ++t, ++st) {
-                if (st == n_stages) {
-                    st = 0;
                     ++k;
                 }
                 float* tp = ring + st * kTile;
@@ -1158,9 +1119,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     }
                     __syncwarp();
                 }
-                if (has_hist) {
-                    // count the tile's ids in 16-bit counters, then the first lane to clear a counter owns that id
-                    // and applies the penalties with its count
+                if (use_table) {
+                    // the tile's generated columns, spread evenly over the lanes by rank (sampler.cpp:23-28)
+                    const uint32_t w_lo = base >> 5, w_hi = min((base + n_t + 31u) >> 5, bm_words);
+                    fix_hits(bitmap, wpre, counts, tp, base, w_lo, w_hi, (uint32_t)wpre[w_lo],
+                             (w_hi < bm_words) ? (uint32_t)wpre[w_hi] : s.n_distinct, lane, 32u, cfg);
+                } else if (has_hist) {
+                    // long history: count the tile's ids in 16-bit counters, then the first lane to clear a
+                    // counter owns that id and applies the penalties with its count
                     for (uint32_t j = lane; j < hlen; j += 32) {
                         const int64_t loc = (int64_t)hist_at(j) - a.id_offset - (int64_t)base;
                         if (loc >= 0 && loc < (int64_t)n_t)
@@ -2080,7 +2046,10 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     if (e != cudaSuccess)
         return e;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(row_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        e = cudaFuncSetAttribute(row_pipeline_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e != cudaSuccess)
+            return e;
+        e = cudaFuncSetAttribute(row_pipeline_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess)
             return e;
         configured[dev] = true;
@@ -2101,7 +2070,9 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     lc.numAttrs = a.overlap != MK_OVERLAP_OFF ? 1u : 0u;
     RowKernelArgs first = a;
     first.pass = 0;
-    e = cudaLaunchKernelEx(&lc, row_pipeline_kernel, first);
+    const bool spec = a.spec_n_pos != 0u;
+    e = spec ? cudaLaunchKernelEx(&lc, row_pipeline_kernel<true>, first)
+             : cudaLaunchKernelEx(&lc, row_pipeline_kernel<false>, first);
     if (e != cudaSuccess)
         return e;
     // top_p alone (make_cfg: need_sum): rows whose nucleus the first launch could not settle are streamed again
@@ -2113,7 +2084,8 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     if (a.mode != kModeVpLocal && kNucleusGuess < a.n_vocab && (a.params_dev || host_need_sum)) {
         RowKernelArgs second = a;
         second.pass = 1;
-        e = cudaLaunchKernelEx(&lc, row_pipeline_kernel, second);
+        e = spec ? cudaLaunchKernelEx(&lc, row_pipeline_kernel<true>, second)
+                 : cudaLaunchKernelEx(&lc, row_pipeline_kernel<false>, second);
     }
     return e;
 }
