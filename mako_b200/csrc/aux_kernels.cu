@@ -344,58 +344,71 @@ __global__ void __launch_bounds__(kPqThreads) pq_resolve_kernel(const PqResolveA
             __syncthreads();
         }
     }
-    if (tid == 0) {
-        // two sequential merges: the float total of the residual, then the walk
+    // The residual max(0, p - q) is zero wherever p is: only the target's candidates matter, in ascending id. Every
+    // thread looks its candidates' drafter probabilities up by binary search (the drafter's list is sorted by id
+    // too) and leaves the residual beside the id; the float total and the walk, sequential by definition, are then
+    // chains one warp runs on values handed round by shuffles.
+    for (uint32_t i = tid; i < np; i += kPqThreads) {
+        const unsigned long long kpi = kp[i];
+        const uint32_t id = (uint32_t)(kpi >> 32);
+        const float pn = __fdiv_rn(__uint_as_float((uint32_t)(kpi & 0xffffffffull)), total_p);
+        uint32_t lo = 0, hi = nq;
+        while (lo < hi) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if ((uint32_t)(kq[mid] >> 32) < id)
+                lo = mid + 1;
+            else
+                hi = mid;
+        }
+        float qn = 0.0f;
+        if (lo < nq && (uint32_t)(kq[lo] >> 32) == id)
+            qn = __fdiv_rn(__uint_as_float((uint32_t)(kq[lo] & 0xffffffffull)), total_q);
+        kp[i] = ((unsigned long long)id << 32) | __float_as_uint(__fsub_rn(pn, qn));
+    }
+    __syncthreads();
+    if (tid < 32) {
+        const uint32_t lane = tid, full = 0xffffffffu;
         float total_r = 0.0f;
         uint32_t n_res = 0;
-        for (int pass = 0; pass < 2; ++pass) {
-            float r = __fmul_rn(a.u_resample[row], total_r);
-            int32_t tok = d, last = d;
-            bool done = false;
-            uint32_t i = 0, j = 0;
-            while ((i < np || j < nq) && !done) {
-                const uint32_t ip = i < np ? (uint32_t)(kp[i] >> 32) : 0xffffffffu;
-                const uint32_t iq = j < nq ? (uint32_t)(kq[j] >> 32) : 0xffffffffu;
-                float pn = 0.0f, qn = 0.0f;
-                uint32_t id;
-                if (ip < iq) {
-                    id = ip;
-                    pn = __fdiv_rn(__uint_as_float((uint32_t)(kp[i] & 0xffffffffull)), total_p);
-                    ++i;
-                } else if (iq < ip) {
-                    id = iq;
-                    qn = __fdiv_rn(__uint_as_float((uint32_t)(kq[j] & 0xffffffffull)), total_q);
-                    ++j;
-                } else {
-                    id = ip;
-                    pn = __fdiv_rn(__uint_as_float((uint32_t)(kp[i] & 0xffffffffull)), total_p);
-                    qn = __fdiv_rn(__uint_as_float((uint32_t)(kq[j] & 0xffffffffull)), total_q);
-                    ++i;
-                    ++j;
+        for (uint32_t base = 0; base < np; base += 32u) {
+            const float res = (base + lane < np) ? __uint_as_float((uint32_t)(kp[base + lane] & 0xffffffffull)) : 0.0f;
+            const int cnt = (int)min(32u, np - base);
+            for (int j = 0; j < cnt; ++j) {
+                const float rj = __shfl_sync(full, res, j);
+                if (rj > 0.0f) {
+                    total_r = __fadd_rn(total_r, rj);
+                    ++n_res;
                 }
-                const float res = __fsub_rn(pn, qn);
-                if (res > 0.0f) {
-                    if (pass == 0) {
-                        total_r = __fadd_rn(total_r, res);
-                        ++n_res;
+            }
+        }
+        float r = __fmul_rn(a.u_resample[row], total_r);
+        int32_t tok = d, last = d;
+        bool done = false;
+        for (uint32_t base = 0; base < np && !done; base += 32u) {
+            const unsigned long long e = (base + lane < np) ? kp[base + lane] : 0ull;
+            const float res = __uint_as_float((uint32_t)(e & 0xffffffffull));
+            const int32_t id = (int32_t)(uint32_t)(e >> 32);
+            const int cnt = (int)min(32u, np - base);
+            for (int j = 0; j < cnt && !done; ++j) {
+                const float rj = __shfl_sync(full, res, j);
+                const int32_t idj = __shfl_sync(full, id, j);
+                if (rj > 0.0f) {
+                    last = idj;
+                    if (r < rj) {
+                        tok = idj;
+                        done = true;
                     } else {
-                        last = (int32_t)id;
-                        if (r < res) {
-                            tok = (int32_t)id;
-                            done = true;
-                        } else {
-                            r = __fsub_rn(r, res);
-                        }
+                        r = __fsub_rn(r, rj);
                     }
                 }
             }
-            if (pass == 1) {
-                if (!done)
-                    tok = last;
-                a.accepted[row] = 0;
-                a.token[row] = n_res ? tok : d;
-                if (a.flags) a.flags[row] = fl;
-            }
+        }
+        if (!done)
+            tok = last;
+        if (lane == 0) {
+            a.accepted[row] = 0;
+            a.token[row] = n_res ? tok : d;
+            if (a.flags) a.flags[row] = fl;
         }
     }
 }

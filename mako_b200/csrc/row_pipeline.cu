@@ -63,8 +63,7 @@ constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates
 #define MK_PREFIX_TILES 4
 #endif
 constexpr int kPrefixTiles = MK_PREFIX_TILES;  // tiles all warps edit before the stream starts (their columns fit 16 bits)
-constexpr int kBins = 2048;     // top_k histogram: 11 leading bits of the order key
-constexpr int kBinShift = 21;
+constexpr int kBins = 2048;     // bins of the top_k histogram (see hist_bin)
 
 // Shared memory of a CTA: this fixed head, then kDynBytes laid out per row. While the row streams: the tables the
 // row needs (generated-column bitmap, per-word ranks, counts; the top_k histogram) and, in all that is left, the
@@ -96,6 +95,40 @@ constexpr uint32_t kOffFinWpre = kOffFinBitmap + kBmWords * 4u;   // kBmWords 16
 constexpr uint32_t kOffFinOrd = kOffFinWpre + kBmWords * 2u;      // kSortCap 16-bit slots
 static_assert(kOffFinOrd + kSortCap * 2u <= kDynBytes, "finish layout fits");
 static_assert(kBins * 4u <= kBmWords * 4u, "mass histogram fits the finish bitmap area");
+
+// Bins of the histogram that bounds the k-th largest element of a row: monotone in the float order, fine where
+// logits live — 32 bins per octave for magnitudes from 2^-10 to 2^8 (a bin is 2.2 % wide), everything smaller or
+// larger folded into the end bins of its sign — so that the bin in which the count from the top reaches k holds few
+// elements beyond the k wanted. Positive values take bins 1024.., negative ones mirror them below; NaN takes bin 0.
+__device__ __forceinline__ uint32_t hist_bin(float v)
+{
+    if (v != v)
+        return 0u;
+    const uint32_t u = __float_as_uint(v), mag = u & 0x7fffffffu;
+    const int e = (int)(mag >> 23) - 117;
+    uint32_t p; // 0..575
+    if (e < 0)
+        p = 0u;
+    else if (e > 17)
+        p = 575u;
+    else
+        p = (uint32_t)e * 32u + ((mag >> 18) & 31u);
+    return (u >> 31) ? 1023u - p : 1024u + p;
+}
+
+// A float no element of bin b is smaller than (a bound from below; b >= 1).
+__device__ __forceinline__ float hist_bin_floor(uint32_t b)
+{
+    if (b >= 1024u) {
+        const uint32_t p = min(b - 1024u, 575u);
+        return p == 0u ? 0.0f : __uint_as_float((((p >> 5) + 117u) << 23) | ((p & 31u) << 18));
+    }
+    const uint32_t p = 1023u - b; // magnitudes of this bin lie below the next bin's start
+    if (p >= 575u)
+        return -__int_as_float(0x7f800000);
+    const uint32_t q = p + 1u;
+    return -__uint_as_float((((q >> 5) + 117u) << 23) | ((q & 31u) << 18));
+}
 
 struct RowCfg {
     float temperature, inv_t, minp_eff, top_p;
@@ -631,7 +664,7 @@ __device__ __noinline__ void mass_cut(Smem& s, float* fh, const uint2* scratch, 
             const float w = wv[k];
             const float qa = exp2f((w - m) * c2); // 0 for the filler
             if (w >= thr_final) {
-                atomicAdd(&fh[order_key(w) >> kBinShift], qa);
+                atomicAdd(&fh[hist_bin(w)], qa);
                 mine += (double)qa;
             } else {
                 low += (double)qa;
@@ -675,9 +708,7 @@ __device__ __noinline__ void mass_cut(Smem& s, float* fh, const uint2* scratch, 
             }
         }
         if (lane == 0 && budget > 0.0 && cut > 0 && cut < kBins) {
-            const float edge = key_to_float((uint32_t)cut << kBinShift);
-            if (edge == edge)
-                s.thr_topk_key = max(s.thr_topk_key, (uint32_t)cut << kBinShift);
+            s.thr_topk_key = max(s.thr_topk_key, order_key(hist_bin_floor((uint32_t)cut)));
         }
     }
     __syncthreads();
@@ -1259,7 +1290,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 #pragma unroll
                         for (int e = 0; e < kEl; ++e)
                             if (w[e] >= thr) {
-                                const uint32_t bin = order_key(w[e]) >> kBinShift;
+                                const uint32_t bin = hist_bin(w[e]);
                                 atomicAdd(&hist[bin], 1u);
                                 top_bin = max(top_bin, bin);
                                 if (collect) {
@@ -1294,7 +1325,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         }
                         // the lowest key of a bin is its smallest float; bin 0 (NaN keys) is never a bound
                         if (lane == 0 && found > 0)
-                            atomicMax(&s.thr_topk_key, (uint32_t)found << kBinShift);
+                            atomicMax(&s.thr_topk_key, order_key(hist_bin_floor((uint32_t)found)));
                     }
                 }
                 if (kSum && cfg.need_sum && best > ninf) {
