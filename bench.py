@@ -487,8 +487,13 @@ def run_other(args, cfg_id: int, dev, timer: Timer, peak: float, peak_kind: str)
         pool = cfg["pool"]
         d = to_device(make_inputs(cfg, 0, 1), dev)[0]
         s = BatchSampler(v, 1, dev.index)
-        g = capture(dev, lambda k: s.sample(d["logits"][k % pool:k % pool + 1], params, d["u"][k % pool:k % pool + 1]))
-        report(workload_name(cfg) + ", one row per launch", timer.run(g.replay, PER_GRAPH, args.steps), 1, 4 * v + 12, 1)
+        s.set_overlap(args.overlap)
+        for split, tag, launches in ((True, ", one row per step split over 37 CTAs", 3),
+                                     (False, ", one row per step as one CTA", 1)):
+            s.set_split(split)
+            g = capture(dev, lambda k: s.sample(d["logits"][k % pool:k % pool + 1], params,
+                                                d["u"][k % pool:k % pool + 1]))
+            report(workload_name(cfg) + tag, timer.run(g.replay, PER_GRAPH, args.steps), 1, 4 * v + 12, launches)
     elif cfg_id in (2, 4):
         n_sets = 8 if cfg_id == 2 else 2
         sets = to_device(make_inputs(cfg, 0, n_sets), dev)

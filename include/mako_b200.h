@@ -126,6 +126,14 @@ int mk_check_sampling(const mk_sampling_params* p);
 #define MK_OVERLAP_STABLE_SIDE_INPUTS 2
 int mk_sampler_set_overlap(mk_sampler* s, int mode);
 
+/* No counterpart in the reference. A sample call of at most 8 rows with one shared parameter set that draws
+ * (temperature > 0) under 1 <= top_k <= 64 leaves the device idle as one CTA per row, so by default it runs as three
+ * launches instead: every row's columns split over up to 64 CTAs that each write the record of a vocabulary shard,
+ * the merge of mk_sampler_vp_merge over the records, and a launch of the one-CTA-per-row kernel that returns at once
+ * for every row except those the merge flagged MK_FLAG_VP_TRUNCATED. Same tokens, probabilities and candidate lists
+ * as the plain path. on = 0 makes every batch run as one CTA per row. */
+int mk_sampler_set_split(mk_sampler* s, int on);
+
 /* Replaces Sampler::sample (sampler.cpp:75-84) for rows->batch rows: u[b] in [0,1) is the uniform the reference
  * would draw from its generator (r = u * total, sampler.cpp:66). One kernel, one pass over the logits. */
 int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, const mk_sample_out* out,

@@ -129,6 +129,7 @@ def _load() -> C.CDLL:
     lib.mk_debug_expf.argtypes = [vp, vp, C.c_uint64, vp]
     lib.mk_debug_set_timing.argtypes = [vp, vp]
     lib.mk_sampler_set_overlap.argtypes = [vp, C.c_int]
+    lib.mk_sampler_set_split.argtypes = [vp, C.c_int]
     lib.mk_debug_withhold_tile.argtypes = [vp, C.c_int, C.c_uint32]
     return lib
 

@@ -11,7 +11,8 @@ namespace mk {
 
 namespace {
 
-constexpr int kMergeThreads = 128;
+constexpr int kMergeThreads = 128;    // a CTA per row of a large batch
+constexpr int kMergeThreadsFew = 512; // a handful of rows: the sort is what takes the time, so more threads on it
 constexpr int kMergeCap = 2048; // n_shards * k
 constexpr uint32_t kShardShift = 26, kIdMask = (1u << kShardShift) - 1u; // sort keys: shard above the token id
 
@@ -42,12 +43,12 @@ __device__ void sort_keys(unsigned long long* keys, uint32_t n2, uint32_t n_thre
 // edited logits by (logit desc, id asc). The merge recomputes exact weights against the global maximum, so a
 // candidate's q is the same float the single-device pipeline computes; only the row total that top_p needs when no
 // other truncation is active comes from the rescaled partial sums, and decisions within 1e-5 of it are flagged.
-__global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeArgs a)
+__global__ void __launch_bounds__(kMergeThreadsFew) vp_merge_kernel(const VpMergeArgs a)
 {
     __shared__ unsigned long long keys[kMergeCap];
     __shared__ uint32_t s_n, s_nfinal;
     __shared__ uint32_t s_shard_in[64];  // entries of each shard that are in the deciding set
-    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, n_thr = blockDim.x;
     const uint32_t rb = vp_record_bytes(a.k);
     const mk_sampling_params prm = a.params_dev ? a.params_dev[row] : a.params;
     const float inv_t = __fdiv_rn(1.0f, prm.temperature);
@@ -57,22 +58,33 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
 
     auto rec = [&](uint32_t g) { return a.gathered + ((size_t)g * a.batch + row) * rb; };
 
+    // the shards' headers and best entries, fetched side by side (one thread per shard): every thread walks them below
+    __shared__ float s_max[64];
+    __shared__ uint32_t s_hdr[64], s_first[64];
+    __shared__ double s_sum[64];
+    if (tid < a.n_shards) {
+        s_max[tid] = *reinterpret_cast<const float*>(rec(tid));
+        s_hdr[tid] = *reinterpret_cast<const uint32_t*>(rec(tid) + 4);
+        s_sum[tid] = *reinterpret_cast<const double*>(rec(tid) + 8);
+        s_first[tid] = reinterpret_cast<const uint2*>(rec(tid) + kVpHeaderBytes)->y;
+    }
+    __syncthreads();
+
     // global maximum and first argmax
     float m = ninf;
     uint32_t arg_id = 0, arg_shard = 0;
     bool any = false, nan0 = false;
     for (uint32_t g = 0; g < a.n_shards; ++g) {
-        const float mg = *reinterpret_cast<const float*>(rec(g));
-        const uint32_t ng = *reinterpret_cast<const uint32_t*>(rec(g) + 4) & 0xffffu;
+        const float mg = s_max[g];
+        const uint32_t ng = s_hdr[g] & 0xffffu;
         if (mg != mg) {
             nan0 = true;
             continue;
         }
         if (ng > 0 && mg > ninf) {
-            const uint2 first = *reinterpret_cast<const uint2*>(rec(g) + kVpHeaderBytes);
             if (!any || mg > m) { // shards ascend in id, so the first shard holding the maximum wins ties
                 m = mg;
-                arg_id = first.y;
+                arg_id = s_first[g];
                 arg_shard = g;
                 any = true;
             }
@@ -108,9 +120,9 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
     // below 2^26, checked by the caller): shards ascend in id, so the order by id is unchanged, and the count of a
     // shard's members in the deciding set below needs no knowledge of how the columns were split.
     if (!nan0) {
-        for (uint32_t e = tid; e < a.n_shards * a.k; e += kMergeThreads) {
+        for (uint32_t e = tid; e < a.n_shards * a.k; e += n_thr) {
             const uint32_t g = e / a.k, i = e % a.k;
-            const uint32_t ng = *reinterpret_cast<const uint32_t*>(rec(g) + 4) & 0xffffu;
+            const uint32_t ng = s_hdr[g] & 0xffffu;
             if (i >= ng)
                 continue;
             const uint2 c = reinterpret_cast<const uint2*>(rec(g) + kVpHeaderBytes)[i];
@@ -139,7 +151,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
     uint32_t n2 = 2;
     while (n2 < n)
         n2 <<= 1;
-    for (uint32_t i = tid; i < n2; i += kMergeThreads) {
+    for (uint32_t i = tid; i < n2; i += n_thr) {
         unsigned long long key = ~0ull;
         if (i < n) {
             const unsigned long long raw = keys[i];
@@ -150,7 +162,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
     }
     __syncthreads();
     if (n > 1)
-        sort_keys(keys, n2, kMergeThreads);
+        sort_keys(keys, n2, n_thr);
 
     if (tid == 0) {
         auto q_at = [&](uint32_t i) -> float {
@@ -171,8 +183,8 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
             if (need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
                 const double c2 = (double)inv_t * 1.4426950408889634;
                 for (uint32_t g = 0; g < a.n_shards; ++g) {
-                    const float mg = *reinterpret_cast<const float*>(rec(g));
-                    const double sg = *reinterpret_cast<const double*>(rec(g) + 8);
+                    const float mg = s_max[g];
+                    const double sg = s_sum[g];
                     if (mg > ninf && sg > 0.0)
                         total += sg * exp2((double)(mg - m) * c2);
                 }
@@ -205,7 +217,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
         for (uint32_t i = 0; i < n_decide; ++i)
             s_shard_in[tag_at(i) >> kShardShift] += 1;
         for (uint32_t g = 0; g < a.n_shards && g < 64; ++g) {
-            const uint32_t hdr = *reinterpret_cast<const uint32_t*>(rec(g) + 4);
+            const uint32_t hdr = s_hdr[g];
             const uint32_t ng = hdr & 0xffffu;
             const bool more = (hdr & 0x40000000u) != 0;
             if ((hdr & 0x80000000u) || (more && ng > 0 && s_shard_in[g] >= ng))
@@ -238,7 +250,7 @@ __global__ void __launch_bounds__(kMergeThreads) vp_merge_kernel(const VpMergeAr
     __syncthreads();
     if (a.cand_ids || a.cand_q) {
         const uint32_t nf = min(s_nfinal, a.cand_cap);
-        for (uint32_t i = tid; i < nf; i += kMergeThreads) {
+        for (uint32_t i = tid; i < nf; i += n_thr) {
             const unsigned long long key = keys[i];
             const uint32_t id = (sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32)) & kIdMask;
             const float q = sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
@@ -252,7 +264,7 @@ cudaError_t launch_vp_merge(const VpMergeArgs& a, cudaStream_t stream)
 {
     if (a.batch == 0)
         return cudaSuccess;
-    vp_merge_kernel<<<a.batch, kMergeThreads, 0, stream>>>(a);
+    vp_merge_kernel<<<a.batch, a.batch <= 16u ? kMergeThreadsFew : kMergeThreads, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

@@ -41,6 +41,7 @@ int cuda_fail(cudaError_t e, const char* what)
 inline uint32_t scratch_cap(uint32_t n_vocab) { return (n_vocab + 3u) & ~3u; }
 
 constexpr uint32_t kPqCap = 4096;      // candidates per list in p/q verification
+constexpr uint32_t kSplitMaxBatch = 8, kSplitMaxShards = 64, kSplitKeys = 1024;
 constexpr uint32_t kMaxTiles = 512, kTile = 4096;
 
 } // namespace
@@ -49,6 +50,8 @@ struct mk_sampler {
     int device = 0;
     uint32_t n_vocab = 0, max_batch = 0;
     uint32_t* scratch = nullptr; // [max_batch][4*n_vocab] words: raw candidates (a row can never overflow it) + sort buffer / a float per column
+    uint32_t* scratch_pq = nullptr; // the same again: p/q verification runs its two row sets side by side
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     // p/q verification lists
     int32_t *p_ids = nullptr, *q_ids = nullptr;
     float *p_q = nullptr, *q_q = nullptr, *p_total = nullptr, *q_total = nullptr, *q_prob = nullptr;
@@ -62,6 +65,10 @@ struct mk_sampler {
     unsigned long long* pick_best = nullptr; // mk_draft_pick: one packed (score, id) maximum per sequence
     unsigned char* stage = nullptr;
     size_t stage_bytes = 0;
+    // small batches under a top_k: every row split over many CTAs (shard records, then the merge)
+    unsigned char* split_records = nullptr; // [kSplitMaxShards][kSplitMaxBatch] records of kVpMaxK entries
+    uint32_t* split_flags = nullptr;        // [kSplitMaxBatch], when the caller asks for no flags
+    int split = 1;                          // 0: every batch runs as one CTA per row
 };
 
 namespace {
@@ -154,6 +161,70 @@ bool all_greedy(const mk_rows* r)
     return !r->params_dev && r->params.temperature <= 0.0f;
 }
 
+// A handful of rows under a top_k leaves most of the device idle when each row is one CTA, and the top_k bound costs
+// that CTA a histogram update per element. Such a batch is split instead: every row's columns go to many CTAs, each
+// writing the record a vocabulary shard writes (maximum, partial sum, its best entries); the merge draws from the
+// records. A row the merge cannot prove complete (VP_TRUNCATED: one shard's whole list inside the deciding set) is
+// run again as one CTA by a follow-up launch that skips every other row, so the results are those of the plain path.
+bool split_eligible(const mk_sampler* s, const mk_rows* r, const mk::RowKernelArgs& a)
+{
+    if (!s->split || r->batch == 0 || r->batch > kSplitMaxBatch || r->params_dev || !a.use_bulk_copy)
+        return false;
+    const mk_sampling_params& p = r->params;
+    if (!(p.temperature > 0.0f) || p.top_k == 0 || p.top_k > mk::kVpMaxK)
+        return false;
+    if (r->n_vocab < 4u * kTile || r->id_offset < 0 || (uint64_t)r->id_offset + r->n_vocab > (1u << 26))
+        return false;
+    return s->timing == nullptr && s->skip_tile == 0xffffffffu;
+}
+
+int sample_split(mk_sampler* s, const mk_rows* rows, mk::RowKernelArgs a, const mk_sample_out* out, cudaStream_t stream)
+{
+    (void)out;
+    const uint32_t n_tiles = (rows->n_vocab + kTile - 1) / kTile;
+    const uint32_t per = (n_tiles + kSplitMaxShards - 1) / kSplitMaxShards; // tiles per shard
+    const uint32_t n_shards = (n_tiles + per - 1) / per;
+    uint32_t k = kSplitKeys / n_shards;
+    k = k > mk::kVpMaxK ? mk::kVpMaxK : (k < 8u ? 8u : k);
+    mk::RowKernelArgs first = a;
+    first.mode = mk::kModeVpLocal;
+    first.split_w = per * kTile;
+    first.vp_records = s->split_records;
+    first.vp_k = k;
+    first.token = nullptr;
+    first.prob = nullptr;
+    first.flags = nullptr;
+    first.n_cand = nullptr;
+    first.cand_ids = nullptr;
+    first.cand_q = nullptr;
+    MK_CUDA(mk::launch_row_kernel(first, rows->batch, stream));
+    mk::VpMergeArgs m;
+    std::memset(&m, 0, sizeof m);
+    m.gathered = s->split_records;
+    m.n_shards = n_shards;
+    m.batch = rows->batch;
+    m.k = k;
+    m.n_vocab_total = rows->n_vocab;
+    m.params = rows->params;
+    m.u = a.u;
+    m.token = a.token;
+    m.prob = a.prob;
+    m.flags = a.flags ? a.flags : s->split_flags;
+    m.n_cand = a.n_cand;
+    m.cand_ids = a.cand_ids;
+    m.cand_q = a.cand_q;
+    m.cand_cap = a.cand_cap;
+    MK_CUDA(mk::launch_vp_merge(m, stream));
+    // the rows the merge reported incomplete, as one CTA each; this launch reads the flags the merge wrote, so it is
+    // never started ahead of it
+    a.overlap = MK_OVERLAP_OFF;
+    a.only_flagged = m.flags;
+    a.only_flagged_mask = MK_FLAG_VP_TRUNCATED;
+    a.flags = m.flags;
+    MK_CUDA(mk::launch_row_kernel(a, rows->batch, stream));
+    return MK_OK;
+}
+
 } // namespace
 
 extern "C" {
@@ -229,6 +300,7 @@ int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t m
             e = cudaMalloc(p, bytes);
     };
     alloc((void**)&s->scratch, b * mk::row_scratch_words(scratch_cap(n_vocab)) * 4);
+    alloc((void**)&s->scratch_pq, b * mk::row_scratch_words(scratch_cap(n_vocab)) * 4);
     alloc((void**)&s->p_ids, b * kPqCap * 4);
     alloc((void**)&s->q_ids, b * kPqCap * 4);
     alloc((void**)&s->p_q, b * kPqCap * 4);
@@ -242,10 +314,16 @@ int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t m
     alloc((void**)&s->q_flags, b * 4);
     alloc((void**)&s->p_tok, b * 4);
     alloc((void**)&s->pick_best, (mk::kDraftPickMaxSeq + 1) * sizeof(unsigned long long)); // maxima + ticket counter
+    alloc((void**)&s->split_records, (size_t)kSplitMaxShards * kSplitMaxBatch * mk::vp_record_bytes(mk::kVpMaxK));
+    alloc((void**)&s->split_flags, kSplitMaxBatch * 4);
     if (e == cudaSuccess)
         e = cudaMemset(s->pick_best, 0, (mk::kDraftPickMaxSeq + 1) * sizeof(unsigned long long));
     if (e == cudaSuccess)
         e = cudaStreamCreateWithFlags(&s->own_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess)
+        e = cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess)
+        e = cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming);
     if (e != cudaSuccess) {
         mk_sampler_destroy(s);
         return cuda_fail(e, "allocating the handle's scratch");
@@ -260,10 +338,15 @@ void mk_sampler_destroy(mk_sampler* s)
         return;
     DeviceGuard g(s->device);
     void* ptrs[] = {s->scratch, s->p_ids, s->q_ids, s->p_q, s->q_q, s->p_total, s->q_total, s->q_prob,
-                    s->p_n,     s->q_n,   s->p_flags, s->q_flags, s->p_tok, s->stage, s->pick_best};
+                    s->p_n,     s->q_n,   s->p_flags, s->q_flags, s->p_tok, s->stage, s->pick_best,
+                    s->split_records, s->split_flags, s->scratch_pq};
     for (void* p : ptrs)
         if (p)
             cudaFree(p);
+    if (s->ev_fork)
+        cudaEventDestroy(s->ev_fork);
+    if (s->ev_join)
+        cudaEventDestroy(s->ev_join);
     if (s->own_stream)
         cudaStreamDestroy(s->own_stream);
     delete s;
@@ -283,6 +366,8 @@ int mk_sampler_sample_batch(mk_sampler* s, const mk_rows* rows, const float* u, 
     fill_out(a, out);
     a.u = u;
     a.mode = mk::kModeSample;
+    if (split_eligible(s, rows, a))
+        return sample_split(s, rows, a, out, (cudaStream_t)stream);
     MK_CUDA(mk::launch_row_kernel(a, rows->batch, (cudaStream_t)stream));
     return MK_OK;
 }
@@ -371,6 +456,12 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
         return fail(MK_ERR_INVALID_ARGUMENT, "three uniforms per row are required");
     DeviceGuard g(s->device);
     cudaStream_t st = (cudaStream_t)stream;
+    // The drafter's rows and the target's rows are independent until the resolve: the target's launches go to the
+    // handle's own stream, forked from and joined back into the caller's (a stream capture follows both arms), so the
+    // few long rows of one set's second launch do not leave the device idle and the two first launches fill it as
+    // one. Each arm has its own candidate scratch.
+    MK_CUDA(cudaEventRecord(s->ev_fork, st));
+    MK_CUDA(cudaStreamWaitEvent(s->own_stream, s->ev_fork, 0));
     // drafter rows: draw the draft token and keep q's list
     mk_rows qrows = *rows;
     qrows.logits = draft_logits;
@@ -398,7 +489,11 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
     a.cand_cap = kPqCap;
     a.total_out = s->p_total;
     a.mode = mk::kModeDistOnly;
-    MK_CUDA(mk::launch_row_kernel(a, rows->batch, st));
+    a.scratch = s->scratch_pq;
+    a.overlap = MK_OVERLAP_OFF; // nothing precedes it in that stream but the fork
+    MK_CUDA(mk::launch_row_kernel(a, rows->batch, s->own_stream));
+    MK_CUDA(cudaEventRecord(s->ev_join, s->own_stream));
+    MK_CUDA(cudaStreamWaitEvent(st, s->ev_join, 0));
     mk::PqResolveArgs r;
     std::memset(&r, 0, sizeof r);
     r.batch = rows->batch;
@@ -673,6 +768,14 @@ int mk_sampler_set_overlap(mk_sampler* s, int mode)
     if (mode != MK_OVERLAP_OFF && mode != MK_OVERLAP_LAUNCH && mode != MK_OVERLAP_STABLE_SIDE_INPUTS)
         return fail(MK_ERR_INVALID_ARGUMENT, "overlap mode %d is none of MK_OVERLAP_*", mode);
     s->overlap = mode;
+    return MK_OK;
+}
+
+int mk_sampler_set_split(mk_sampler* s, int on)
+{
+    if (!s)
+        return fail(MK_ERR_INVALID_ARGUMENT, "null sampler handle");
+    s->split = on ? 1 : 0;
     return MK_OK;
 }
 

@@ -127,4 +127,13 @@ __device__ __forceinline__ float key_to_float(uint32_t k)
     return __uint_as_float(u);
 }
 
+// 2^x on the special-function unit: relative error about 2^-22, results below 2^-126 flushed to zero, 2^-inf = +0.
+// For sums whose error margin is reported with them; never for a weight the reference computes with expf.
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 } // namespace mk

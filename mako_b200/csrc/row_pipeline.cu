@@ -58,7 +58,7 @@ constexpr int kBmWords = 5120;  // history bitmap: one bit per column, vocabular
 constexpr uint32_t kMaxBitmapVocab = kBmWords * 32u;
 constexpr int kSortCap = 8192;  // 64-bit sort keys: they take the ring (64 KB) once the streaming is over
 constexpr uint32_t kBarSort = 3;         // named barrier of the sorting warps
-constexpr uint32_t kNucleusGuess = 256; // top_p alone, first launch: candidates kept
+constexpr uint32_t kNucleusGuess = 24;  // top_p alone, first launch: the largest elements kept (the one-warp finish takes 32 candidates)
 #ifndef MK_PREFIX_TILES
 #define MK_PREFIX_TILES 4
 #endif
@@ -80,6 +80,7 @@ struct __align__(128) Smem {
     uint32_t abort_flag;
     uint32_t nan0;                  // column 0 (token id 0) is NaN: the reference's max_element keeps it
     uint32_t hi_group;              // highest non-empty group of 32 histogram bins
+    uint32_t first_tile_warps;      // reader warps whose first-tile maxima are in the histogram
     uint32_t n_final;
     uint32_t flags;
     uint32_t n_distinct;            // distinct special columns (generated or biased)
@@ -636,80 +637,128 @@ __device__ __noinline__ uint32_t wide_top_p(Smem& s, const unsigned long long* k
     return k | (unsure ? 0x80000000u : 0u);
 }
 
+// A sweep of the whole CTA over a row's collected (logit, column) pairs in global memory, two pairs per 16-byte load
+// and eight loads of every thread in flight: such a list is read at the pace of its loads' latency, so the bytes in
+// flight are what counts. `f(logit bits, column)` is called once per pair, in no particular order.
+template <class F>
+__device__ __forceinline__ void for_each_collected(const uint2* scratch, uint32_t n_raw, F&& f)
+{
+    const uint4* const s4 = reinterpret_cast<const uint4*>(scratch); // a row's scratch starts on a 16-byte boundary
+    const uint32_t n_pairs = (n_raw + 1u) >> 1;
+    for (uint32_t p0 = threadIdx.x; p0 < n_pairs; p0 += 8u * kThreads) {
+        uint4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t p = p0 + (uint32_t)k * kThreads;
+            v[k] = (p < n_pairs) ? s4[p] : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t p = p0 + (uint32_t)k * kThreads;
+            if (p < n_pairs) {
+                f(v[k].x, v[k].y);
+                if (2u * p + 1u < n_raw)
+                    f(v[k].z, v[k].w);
+            }
+        }
+    }
+}
+
 // top_p alone, a long collected list: the nucleus leaves out a tail of mass (1 - top_p) * total. Everything that was
 // not collected belongs to that tail; collected elements can join it from the bottom for as long as the tail stays
 // within the budget. Approximate weights decide the cut (with margins) and raise s.thr_topk_key; the nucleus itself
 // is then computed from exact weights, and a cut that turns out too tight is reported. Whole CTA. (Out of line, like
 // the other steps few rows need: what the common row runs stays short and contiguous.)
-__device__ __noinline__ void mass_cut(Smem& s, float* fh, const uint2* scratch, uint32_t n_raw, float thr_final, float m,
-                                      float inv_t, float top_p, double total_approx)
+//
+// The cut is found in one sweep over the collected logits that sorts their approximate weights into kCutBins equal
+// steps of the logit between the bound in force and the row maximum (a step is a fraction of a logit: what a finer
+// cut would still drop is a few per cent of the list; the loop below would refine it, and one sweep of a long list
+// costs more than that). Every thread keeps its own bins (`ph`, kCutBins x kThreads floats, the thread index innermost: no two lanes
+// share a bank), so nothing is atomic; the bins are summed over the threads afterwards. A logit below the value
+// lo + c * width has a bin index of at most c (the index is monotone in the logit), so "everything below that value"
+// weighs no more than the mass below `lo` plus bins 0..c: the largest c for which that fits the budget is taken.
+constexpr int kCutBins = 64;
+static_assert((uint32_t)kCutBins * kThreads * 4u + (uint32_t)kCutBins * 8u <= kDynBytes, "the cut's bins fit");
+__device__ __noinline__ void mass_cut(Smem& s, unsigned char* dyn, const uint2* scratch, uint32_t n_raw, float thr_final,
+                                      float m, float inv_t, float top_p, double total_approx)
 {
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-        for (uint32_t i = tid; i < kBins; i += kThreads)
-        fh[i] = 0.0f;
-    if (tid == 0)
-        s.warp_sum[0] = s.warp_sum[1] = 0.0;
-    __syncthreads();
+    float* const ph = reinterpret_cast<float*>(dyn);
+    double* const bin_total = reinterpret_cast<double*>(dyn + (size_t)kCutBins * kThreads * 4u);
     const float c2 = inv_t * 1.4426950408889634f;
-    double mine = 0.0, low = 0.0;
-    for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
-        float wv[4]; // four loads in flight
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const uint32_t i = i0 + (uint32_t)k * kThreads;
-            wv[k] = (i < n_raw) ? __uint_as_float(scratch[i].x) : -__int_as_float(0x7f800000);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float w = wv[k];
-            const float qa = exp2f((w - m) * c2); // 0 for the filler
-            if (w >= thr_final) {
-                atomicAdd(&fh[hist_bin(w)], qa);
-                mine += (double)qa;
-            } else {
-                low += (double)qa;
+    float lo = thr_final, hi = m;
+    double budget = 0.0;
+    for (int sweep = 0; sweep < 1; ++sweep) {
+        if (!(hi > lo)) // also false for NaN
+            break;
+        const float width = (hi - lo) * (1.0f / (float)kCutBins);
+        const float scale = (float)kCutBins / (hi - lo);
+        if (!(width > 0.0f) || !(scale < __int_as_float(0x7f800000)))
+            break;
+        for (int b = 0; b < kCutBins; ++b)
+            ph[b * kThreads + tid] = 0.0f;
+        if (tid == 0)
+            s.warp_sum[0] = s.warp_sum[1] = 0.0;
+        __syncthreads();
+        double all = 0.0, low = 0.0; // every collected element; those below `lo`
+        float all_f = 0.0f, low_f = 0.0f; // a thread's share: at most a few hundred terms each
+        for_each_collected(scratch, n_raw, [&](uint32_t bits, uint32_t) {
+            const float w = __uint_as_float(bits);
+            const float qa = ex2_approx((w - m) * c2);
+            all_f += qa;
+            if (w < lo) {
+                low_f += qa;
+            } else if (w < hi) {
+                const int b = min(kCutBins - 1, (int)((w - lo) * scale));
+                ph[b * kThreads + tid] += qa;
             }
-        }
-    }
+        });
+        all = (double)all_f;
+        low = (double)low_f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        mine += __shfl_xor_sync(0xffffffffu, mine, o);
-        low += __shfl_xor_sync(0xffffffffu, low, o);
-    }
-    if (lane == 0) {
-        atomicAdd(&s.warp_sum[0], mine);
-        atomicAdd(&s.warp_sum[1], low);
-    }
-    __syncthreads();
-    if (warp == 0) {
-        const double collected = s.warp_sum[0];
-        const double outside = total_approx + s.warp_sum[1]; // never collected, or below the final bound
-        const double total_est = collected + outside;
-        const double budget = (1.0 - (double)top_p) * total_est * 0.999 - (outside + 1e-5 * total_est);
-        double cum = 0.0;
-        int cut = 0; // elements in bins below `cut` may be dropped
-        bool stop = false;
-        for (int g = 0; g < kBins / 32 && !stop; ++g) {
-            const float v = fh[g * 32 + lane];
-            double pre = (double)v; // inclusive prefix over lanes
+        for (int o = 16; o > 0; o >>= 1) {
+            all += __shfl_xor_sync(0xffffffffu, all, o);
+            low += __shfl_xor_sync(0xffffffffu, low, o);
+        }
+        if (lane == 0) {
+            atomicAdd(&s.warp_sum[0], all);
+            atomicAdd(&s.warp_sum[1], low);
+        }
+        __syncthreads();
+        for (int b = (int)warp; b < kCutBins; b += kThreads / 32) { // a warp per bin: the threads' shares, summed
+            double t = 0.0;
+            for (uint32_t j = lane; j < (uint32_t)kThreads; j += 32u)
+                t += (double)ph[b * kThreads + j];
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const double y = __shfl_up_sync(0xffffffffu, pre, o);
-                if ((int)lane >= o)
-                    pre += y;
-            }
-            const uint32_t okm = __ballot_sync(0xffffffffu, cum + pre <= budget);
-            if (okm == 0xffffffffu) {
-                cut = (g + 1) * 32;
-                cum += __shfl_sync(0xffffffffu, pre, 31);
-            } else {
-                cut = g * 32 + __ffs(~okm) - 1; // first bin that no longer fits
-                stop = true;
-            }
+            for (int o = 16; o > 0; o >>= 1)
+                t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (lane == 0)
+                bin_total[b] = t;
         }
-        if (lane == 0 && budget > 0.0 && cut > 0 && cut < kBins) {
-            s.thr_topk_key = max(s.thr_topk_key, order_key(hist_bin_floor((uint32_t)cut)));
+        __syncthreads();
+        if (sweep == 0) {
+            const double collected = s.warp_sum[0];
+            const double total_est = collected + total_approx; // total_approx: what was never collected
+            budget = (1.0 - (double)top_p) * total_est * 0.999 - (total_approx + 1e-5 * total_est);
         }
+        // every thread walks the 64 bin totals itself (the same values, the same result)
+        double upto = s.warp_sum[1];
+        int cut = -1; // the largest c whose bins 0..c, with everything below `lo`, fit the budget
+        for (int b = 0; b < kCutBins; ++b) {
+            upto += bin_total[b];
+            if (upto <= budget)
+                cut = b;
+            else
+                break;
+        }
+        __syncthreads(); // bin_total, warp_sum and ph are written again by the next sweep and the caller
+        if (!(budget > 0.0) || cut < 0)
+            break; // nothing more can be left out at this resolution
+        const float new_lo = lo + (float)cut * width;
+        hi = fminf(hi, lo + (float)(cut + 2) * width);
+        lo = new_lo;
+        if (tid == 0 && lo > thr_final)
+            s.thr_topk_key = max(s.thr_topk_key, order_key(lo));
     }
     __syncthreads();
 }
@@ -727,12 +776,21 @@ __device__ __noinline__ const unsigned long long* long_sort(Smem& s, unsigned lo
     if (tid == 0)
         s.nsurv = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < n_raw; i += kThreads) { // survivors, compacted, as sort keys
-        const uint2 c = scratch[i];
-        if (__uint_as_float(c.x) >= thr2) {
-            const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), inv_t));
-            if (q >= minp_eff && q > 0.0f)
-                KA[atomicAdd(&s.nsurv, 1u)] = pack_by_weight(q, c.y);
+    for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) { // survivors, compacted, as sort keys
+        uint2 cv[4]; // four loads in flight
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = i0 + (uint32_t)k * kThreads;
+            cv[k] = (i < n_raw) ? scratch[i] : make_uint2(0xff800000u, 0u); // filler: -inf, below any bound
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint2 c = cv[k];
+            if (__uint_as_float(c.x) >= thr2) {
+                const float q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), inv_t));
+                if (q >= minp_eff && q > 0.0f)
+                    KA[atomicAdd(&s.nsurv, 1u)] = pack_by_weight(q, c.y);
+            }
         }
     }
     __syncthreads();
@@ -765,7 +823,9 @@ __device__ __noinline__ const unsigned long long* long_sort(Smem& s, unsigned lo
 
 // kSpec: the rows of a speculative round (row = sequence * n_pos + position); compiled apart, so that the plain
 // kernel carries none of its bookkeeping.
-template <bool kSpec>
+// kSplit: a launch whose grid has a second dimension over column shards of every row (shard records of a few rows
+// split over many CTAs: the single-row latency path).
+template <bool kSpec, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKernelArgs a)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -774,9 +834,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     const uint32_t row = blockIdx.x;
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5, lane = tid & 31;
-    const uint32_t V = a.n_vocab;
+    // a split launch: CTA (row, g) takes columns [g * split_w, ...) of the row, and that share of the row's scratch
+    const uint32_t col0 = kSplit ? blockIdx.y * a.split_w : 0u;
+    const uint32_t V = kSplit ? min(a.split_w, a.n_vocab - col0) : a.n_vocab;
+    const int32_t id_off = kSplit ? a.id_offset + (int32_t)col0 : a.id_offset;
+    const uint32_t scratch_cap = kSplit ? min(a.split_w, a.scratch_cap - col0) : a.scratch_cap;
     const uint32_t n_tiles = (V + kTile - 1) / kTile;
-    const float* __restrict__ lrow = a.logits + (size_t)row * a.ld;
+    const float* __restrict__ lrow = a.logits + (size_t)row * a.ld + col0;
     // A speculative round (src/gen/session.cpp:451-506): row = sequence * n_pos + position. Position j < n_pos - 1
     // verifies draft j, the last one is the bonus row and is sampled; the penalties of position j count the sequence's
     // history plus drafts 0..j-1 (each accepted draft is emit()ted before the next row is looked at, :491); a forced
@@ -836,18 +900,18 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 #pragma unroll
         for (int i = 0; i < kHistPerThread; ++i) {
             const uint32_t j = (uint32_t)i * kThreads + tid;
-            hc[i] = (j < hlen) ? (uint32_t)hist_at(j) - (uint32_t)a.id_offset : 0xffffffffu;
+            hc[i] = (j < hlen) ? (uint32_t)hist_at(j) - (uint32_t)id_off : 0xffffffffu;
         }
     }
     const RowCfg cfg = make_cfg(prm, V, mode, a.vp_k, a.pass);
-    const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld : nullptr;
+    const uint32_t* __restrict__ mrow = a.mask ? a.mask + (size_t)row * a.mask_ld + (col0 >> 5) : nullptr;
     // Per-row scratch, 16 bytes per column: scratch_cap raw candidates (logit bits, column) — sorted in place as
     // 64-bit keys by the large sorted-list path — then as much again: the merge sort's second buffer, or (large
     // unsorted lists) one float per column.
-    uint32_t* const row_scratch = a.scratch + (size_t)row * row_scratch_words(a.scratch_cap);
+    uint32_t* const row_scratch = a.scratch + (size_t)row * row_scratch_words(a.scratch_cap) + 4ull * col0;
     uint2* __restrict__ scratch = reinterpret_cast<uint2*>(row_scratch);
-    float* __restrict__ qrow = reinterpret_cast<float*>(row_scratch + 2u * a.scratch_cap);
-    uint32_t* const again = row_scratch + 4u * a.scratch_cap; // set by the first launch: this row wants the second pass
+    float* __restrict__ qrow = reinterpret_cast<float*>(row_scratch + 2u * scratch_cap);
+    uint32_t* const again = row_scratch + 4u * scratch_cap; // set by the first launch: this row wants the second pass
     if (spec && a.spec_forced) {
         const int32_t f = __ldg(a.spec_forced + row);
         if (f >= 0) { // the sampler is bypassed: the token is the forced one, a draft is kept only if it matches
@@ -865,6 +929,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     if (a.pass == 1 && again[0] == 0u)
         return;
+    if (a.only_flagged && !(a.only_flagged[row] & a.only_flagged_mask))
+        return; // a follow-up launch for the rows an earlier step reported: the others are done
     // ---- shared-memory layout of the streaming phase ---------------------------------------------------------------
     const uint32_t bm_words = (V + 31u) / 32u;
     unsigned char* const dyn = smem_raw + kHeadBytes;
@@ -898,6 +964,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         s.abort_flag = 0;
         s.nan0 = 0;
         s.hi_group = 0;
+        s.first_tile_warps = 0;
         s.n_final = 0;
         s.flags = 0;
         s.n_distinct = 0;
@@ -1013,7 +1080,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
     }
     griddep_launch_dependents();
-    if (a.pass == 0 && tid == 0)
+    if (a.pass == 0 && tid == 0 && !kSplit)
         again[0] = 0u;
     float u_row = a.u ? __ldg(a.u + (spec ? 0u : row)) : 0.0f;
     float u2_row = a.u2 ? __ldg(a.u2 + row) : 0.0f;
@@ -1040,7 +1107,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         if (nb > 0) {
             for (uint32_t j = tid; j < nb; j += kThreads) {
                 const mk_bias be = brow[j];
-                const int64_t loc = (int64_t)be.id - a.id_offset;
+                const int64_t loc = (int64_t)be.id - id_off;
                 if (be.id >= 0 && loc >= 0 && loc < (int64_t)span)
                     ring[loc] = __fadd_rn(ring[loc], be.value); // stages 0.. are contiguous
             }
@@ -1144,7 +1211,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 if (nb > 0) {
                     for (uint32_t j = lane; j < nb; j += 32) {
                         const mk_bias be = brow[j];
-                        const int64_t loc = (int64_t)be.id - a.id_offset - (int64_t)base;
+                        const int64_t loc = (int64_t)be.id - id_off - (int64_t)base;
                         if (be.id >= 0 && loc >= 0 && loc < (int64_t)n_t)
                             tp[loc] = __fadd_rn(tp[loc], be.value);
                     }
@@ -1159,13 +1226,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     // long history: count the tile's ids in 16-bit counters, then the first lane to clear a
                     // counter owns that id and applies the penalties with its count
                     for (uint32_t j = lane; j < hlen; j += 32) {
-                        const int64_t loc = (int64_t)hist_at(j) - a.id_offset - (int64_t)base;
+                        const int64_t loc = (int64_t)hist_at(j) - id_off - (int64_t)base;
                         if (loc >= 0 && loc < (int64_t)n_t)
                             atomicAdd(&cnt[(uint32_t)loc >> 1], 1u << (((uint32_t)loc & 1u) * 16u));
                     }
                     __syncwarp();
                     for (uint32_t j = lane; j < hlen; j += 32) {
-                        const int64_t loc64 = (int64_t)hist_at(j) - a.id_offset - (int64_t)base;
+                        const int64_t loc64 = (int64_t)hist_at(j) - id_off - (int64_t)base;
                         if (loc64 >= 0 && loc64 < (int64_t)n_t) {
                             const uint32_t loc = (uint32_t)loc64, sh = (loc & 1u) * 16u;
                             const uint32_t old = atomicAnd(&cnt[loc >> 1], ~(0xffffu << sh));
@@ -1280,33 +1347,37 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
                 float thr = keep_threshold(cfg, key_to_float(*(volatile uint32_t*)&s.m_key));
                 if (kHist && cfg.hist_mode) {
-                    // top_k bound: histogram of the keys seen so far that are still above the current bound; the bin
-                    // where the count from the top reaches k bounds the k-th largest from below.
+                    // top_k bound. Every thread enters the largest of its 16 elements of the tile, if that is still at
+                    // or above the bound in force, into a histogram of the value range: the maxima of different
+                    // threads and tiles are different elements, so the bin in which the count from the top reaches k
+                    // bounds the k-th largest element of the row from below — one histogram update for 16 elements,
+                    // and a bound nearly as tight as a histogram of every element gives (the k largest rarely share
+                    // a thread's 16 columns).
                     thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
                     if (tm >= thr) {
-                        // counted and, in the same pass, appended: the bound in force before this tile's rescan is a
-                        // valid one too (bounds only rise), and one pass over the 16 elements costs half of two
-                        uint32_t top_bin = 0;
-#pragma unroll
-                        for (int e = 0; e < kEl; ++e)
-                            if (w[e] >= thr) {
-                                const uint32_t bin = hist_bin(w[e]);
-                                atomicAdd(&hist[bin], 1u);
-                                top_bin = max(top_bin, bin);
-                                if (collect) {
-                                    const uint32_t slot = atomicAdd(&s.ncand, 1u);
-                                    if (slot < a.scratch_cap)
-                                        scratch[slot] = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-                                }
-                            }
-                        if ((top_bin >> 5) > *(volatile uint32_t*)&s.hi_group)
-                            atomicMax(&s.hi_group, top_bin >> 5);
+                        const uint32_t bin = hist_bin(tm);
+                        atomicAdd(&hist[bin], 1u);
+                        if ((bin >> 5) > *(volatile uint32_t*)&s.hi_group)
+                            atomicMax(&s.hi_group, bin >> 5);
+                    }
+                    __syncwarp();
+                    // The first tile would be kept whole (no bound exists while it is read), so its 256 thread maxima
+                    // give a first bound before anything is kept: the warps wait for one another's maxima — a bounded
+                    // wait; a warp that gives up merely keeps more than it had to — and every warp reads the bound off.
+                    if (t == 0) {
+                        __threadfence_block();
+                        if (lane == 0) {
+                            atomicAdd(&s.first_tile_warps, 1u);
+                            for (uint32_t probe = 0; probe < (1u << 12); ++probe)
+                                if (*(volatile uint32_t*)&s.first_tile_warps >= (uint32_t)(kReaders / 32))
+                                    break;
+                        }
+                        __syncwarp();
                     }
                     // One reader warp per tile rescans the histogram and raises the bound; nobody waits for it. Counts
                     // only grow and every count is an element at or above its bin's edge, so a bound read from a
                     // histogram that other warps are still adding to has its k elements all the same.
-                    __syncwarp();
-                    if (rwarp == (t % (kReaders / 32))) {
+                    if (t == 0 || rwarp == (t % (kReaders / 32))) {
                         uint32_t cum = 0;
                         int found = -1;
                         for (int g = (int)*(volatile uint32_t*)&s.hi_group; g >= 0 && found < 0; --g) {
@@ -1326,6 +1397,19 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         // the lowest key of a bin is its smallest float; bin 0 (NaN keys) is never a bound
                         if (lane == 0 && found > 0)
                             atomicMax(&s.thr_topk_key, order_key(hist_bin_floor((uint32_t)found)));
+                        if (t == 0) {
+                            __syncwarp();
+                            thr = fmaxf(thr, key_to_float(*(volatile uint32_t*)&s.thr_topk_key));
+                        }
+                    }
+                    if (collect && tm >= thr) {
+#pragma unroll
+                        for (int e = 0; e < kEl; ++e)
+                            if (w[e] >= thr) {
+                                const uint32_t slot = atomicAdd(&s.ncand, 1u);
+                                if (slot < scratch_cap)
+                                    scratch[slot] = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
+                            }
                     }
                 }
                 if (kSum && cfg.need_sum && best > ninf) {
@@ -1337,7 +1421,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     float p = 0.0f;
 #pragma unroll
                     for (int e = 0; e < kEl; ++e)
-                        p += (sum_all || w[e] < thr) ? exp2f((w[e] - best) * c2) : 0.0f;
+                        p += (sum_all || w[e] < thr) ? ex2_approx((w[e] - best) * c2) : 0.0f;
                     sum_acc += (double)p;
                 }
                 if (!(kHist && cfg.hist_mode) && collect) {
@@ -1366,7 +1450,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 #pragma unroll
                             for (int e = 0; e < kEl; ++e)
                                 if (w[e] >= thr) {
-                                    if (slot < a.scratch_cap)
+                                    if (slot < scratch_cap)
                                         scratch[slot] = make_uint2(__float_as_uint(w[e]),
                                                                    base + (e >> 2) * 1024 + rt * 4 + (e & 3));
                                     ++slot;
@@ -1378,7 +1462,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                             if (w[e] >= thr) {
                                 const uint32_t slot = atomicAdd(&s.ncand, 1u);
                                 const uint2 c = make_uint2(__float_as_uint(w[e]), base + (e >> 2) * 1024 + rt * 4 + (e & 3));
-                                if (slot < a.scratch_cap)
+                                if (slot < scratch_cap)
                                     scratch[slot] = c;
                             }
                     }
@@ -1431,6 +1515,33 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (mrow && !any_finite && !s.nan0)
         flags |= MK_FLAG_ALL_MASKED;
 
+    // need_sum: weight of the uncollected tail (the whole row for a shard record), relative to the row maximum:
+    // sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
+    double total_approx = 0.0;
+    if (cfg.need_sum) {
+        double part = 0.0;
+        if (warp > kFixers / 32) {
+            const float c2 = cfg.inv_t * 1.4426950408889634f;
+            if (best > -__int_as_float(0x7f800000) && sum_acc > 0.0)
+                part += sum_acc * exp2((double)(best - m) * (double)c2);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0)
+                s.warp_sum[warp] = part;
+        } else {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0)
+                s.warp_sum[warp] = part;
+        }
+        __syncthreads();
+        for (int i = 0; i < kThreads / 32; ++i)
+            total_approx += s.warp_sum[i];
+        __syncthreads(); // warp_sum is written again below
+    }
+
     // ---- the short finish: what nearly every row takes ---------------------------------------------------------
     // Few collected elements, at most 32 of them candidates, no row total beyond their own: one warp does it all in
     // registers — exact weights, a 32-key sorting network over the lanes, top_k / top_p / total / draw as sequential
@@ -1439,14 +1550,17 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // is short and contiguous; every other row falls through to the general finish below, which recomputes from the
     // collected elements.
     constexpr uint32_t kFastRaw = 256;
-    if (mode != kModeVpLocal && !cfg.greedy && !cfg.need_sum && !s.nan0 && s.ncand <= kFastRaw &&
-        s.ncand <= a.scratch_cap) {
-        if (warp == 0) {
+    if (mode != kModeVpLocal && !cfg.greedy && !s.nan0 && s.ncand <= kFastRaw && s.ncand <= scratch_cap) {
+        // Compiled twice: rows whose total is the candidates' own (nearly all) run code that knows nothing of the
+        // row total of top_p alone.
+        auto short_finish = [&](auto row_total_tag) {
+            constexpr bool kRowTotal = decltype(row_total_tag)::value;
             const uint32_t full = 0xffffffffu;
             const uint32_t n_raw = s.ncand;
             const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
             unsigned long long* const fkeys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
             uint32_t n = 0;
+            double sum_kept = 0.0, sum_rest = 0.0; // top_p alone: exact weights at or above the bound, the others
             uint2 craw[kFastRaw / 32]; // all requested at once: one trip to memory under load, not one per chunk
 #pragma unroll
             for (uint32_t i = 0; i < kFastRaw / 32; ++i)
@@ -1457,8 +1571,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     break;
                 const uint2 c = craw[i];
                 float q = 0.0f;
-                if (__uint_as_float(c.x) >= thr_final)
+                if (__uint_as_float(c.x) >= thr_final) {
                     q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
+                    if (kRowTotal && q == q)
+                        sum_kept += (double)q;
+                } else if (kRowTotal) {
+                    // collected while the bound was lower: part of the row total, never a candidate
+                    sum_rest += (double)ex2_approx((__uint_as_float(c.x) - m) * (cfg.inv_t * 1.4426950408889634f));
+                }
                 const bool ok = q >= cfg.minp_eff && q > 0.0f; // false for NaN
                 const uint32_t bal = __ballot_sync(full, ok);
                 const uint32_t pos = n + (uint32_t)__popc(bal & ((1u << lane) - 1u));
@@ -1469,6 +1589,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             __syncwarp();
             if (n <= 32u) {
                 uint32_t fl = flags;
+                bool retry = false;
                 if (n == 0) { // sampler.cpp:37-38
                     fl |= MK_FLAG_NO_CANDIDATE;
                     if (lane == 0)
@@ -1512,10 +1633,25 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     n = cfg.top_k;
                 }
                 if (cfg.use_topp) { // sampler.cpp:44-61, sequentially
-                    double total_d = 0.0;
-                    for (uint32_t j = 0; j < n; ++j)
-                        total_d += (double)__shfl_sync(full, q, (int)j);
-                    const double band = 0x1p-40 * total_d, want = (double)cfg.top_p * total_d;
+                    double total_d = 0.0, band;
+                    // top_p alone: the total covers every column — exact weights of what was kept, the streamed sum
+                    // and the approximations above for the rest — and carries the margin of the approximate part
+                    const bool row_total = kRowTotal && !(fl & MK_FLAG_NO_CANDIDATE);
+                    if (row_total) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            sum_kept += __shfl_xor_sync(full, sum_kept, o);
+                            sum_rest += __shfl_xor_sync(full, sum_rest, o);
+                        }
+                        const double rest = total_approx + sum_rest;
+                        total_d = sum_kept + rest;
+                        band = 1e-5 * rest + 0x1p-40 * total_d;
+                    } else {
+                        for (uint32_t j = 0; j < n; ++j)
+                            total_d += (double)__shfl_sync(full, q, (int)j);
+                        band = 0x1p-40 * total_d;
+                    }
+                    const double want = (double)cfg.top_p * total_d;
                     double run = 0.0, prev = 0.0;
                     uint32_t k = 0;
                     for (uint32_t j = 0; j < n && run < want; ++j) {
@@ -1523,8 +1659,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         run += (double)__shfl_sync(full, q, (int)j);
                         k = j + 1u;
                     }
-                    if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
-                        fl |= MK_FLAG_GUARD_BAND;
+                    if ((row_total && run < want) ||
+                        (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))) {
+                        if (cfg.optimistic)
+                            retry = true; // what was kept does not settle the nucleus: the second pass will
+                        else
+                            fl |= MK_FLAG_GUARD_BAND;
+                    }
                     n = max(k, 1u);
                 }
                 if (lane >= n)
@@ -1533,13 +1674,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 for (uint32_t j = 0; j < n; ++j)
                     total = __fadd_rn(total, __shfl_sync(full, q, (int)j));
                 const int32_t draft = (mode == kModeVerify) ? draft_row : -1;
-                const uint32_t dm = __ballot_sync(full, draft >= 0 && lane < n && (int32_t)col + a.id_offset == draft);
+                const uint32_t dm = __ballot_sync(full, draft >= 0 && lane < n && (int32_t)col + id_off == draft);
                 const uint32_t draft_idx = dm ? (uint32_t)__ffs((int)dm) - 1u : 0xffffffffu;
                 const float q_draft = dm ? __shfl_sync(full, q, (int)draft_idx) : 0.0f;
                 int32_t tok = -1, acc = 0;
                 float prob = 0.0f;
                 if (mode == kModeDistOnly) {
-                    tok = (int32_t)__shfl_sync(full, col, 0) + a.id_offset;
+                    tok = (int32_t)__shfl_sync(full, col, 0) + id_off;
                     prob = __fdiv_rn(__shfl_sync(full, q, 0), total);
                 } else {
                     uint32_t skip_idx = 0xffffffffu;
@@ -1580,12 +1721,14 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                                 r = __fsub_rn(r, qj);
                             }
                         }
-                        tok = (int32_t)__shfl_sync(full, col, (int)hit) + a.id_offset;
+                        tok = (int32_t)__shfl_sync(full, col, (int)hit) + id_off;
                         prob = __fdiv_rn(q_hit, walk_total);
                     }
                 }
                 if (lane == 0) {
-                    if (a.token) a.token[row] = tok;
+                    if (retry)
+                        again[0] = 1u; // every output of this row is written again by the second pass
+                    if (a.token) a.token[row] = retry ? -1 : tok;
                     if (a.prob) a.prob[row] = prob;
                     if (a.flags) a.flags[row] = fl;
                     if (a.n_cand) a.n_cand[row] = n;
@@ -1595,12 +1738,18 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                         a.timing[(size_t)row * 64 + 3] = global_ns();
                 }
                 if (lane < min(n, a.cand_cap)) {
-                    if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + lane] = (int32_t)col + a.id_offset;
+                    if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + lane] = (int32_t)col + id_off;
                     if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + lane] = q;
                 }
             }
             if (lane == 0)
                 s.n_final = (n <= 32u) ? 1u : 0u; // 1: the row is done
+        };
+        if (warp == 0) {
+            if (cfg.need_sum)
+                short_finish(std::true_type{});
+            else
+                short_finish(std::false_type{});
         }
         __syncthreads();
         if (s.n_final)
@@ -1610,37 +1759,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             s.n_final = 0;
     }
 
-    // need_sum: weight of the uncollected tail (the whole row for a shard record), relative to the row maximum:
-    // sum over reader threads of sum_acc * exp2((best - m) * c2), fixed order
-    double total_approx = 0.0;
-    if (cfg.need_sum) {
-        double part = 0.0;
-        if (warp > kFixers / 32) {
-            const float c2 = cfg.inv_t * 1.4426950408889634f;
-            if (best > -__int_as_float(0x7f800000) && sum_acc > 0.0)
-                part += sum_acc * exp2((double)(best - m) * (double)c2);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
-                part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (lane == 0)
-                s.warp_sum[warp] = part;
-        } else {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
-                part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (lane == 0)
-                s.warp_sum[warp] = part;
-        }
-        __syncthreads();
-        for (int i = 0; i < kThreads / 32; ++i)
-            total_approx += s.warp_sum[i];
-        __syncthreads(); // warp_sum is written again below
-    }
-
     if (mode == kModeVpLocal) {
         // Shard record: header {max, n, sum} then the k best (logit, global id), by (logit desc, id asc).
         unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
-        const uint32_t n_all = min(s.ncand, a.scratch_cap);
+        const uint32_t n_all = min(s.ncand, scratch_cap);
         const float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
         for (uint32_t i = tid; i < n_all; i += kThreads) {
             const uint2 c = scratch[i];
@@ -1652,7 +1774,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         }
         __syncthreads();
         const uint32_t n_raw = min(s.nsurv, (uint32_t)kSortCap);
-        const bool over = s.nsurv > (uint32_t)kSortCap || s.ncand > a.scratch_cap;
+        const bool over = s.nsurv > (uint32_t)kSortCap || s.ncand > scratch_cap;
         uint32_t n2 = 2;
         while (n2 < n_raw)
             n2 <<= 1;
@@ -1660,7 +1782,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             keys[i] = ~0ull;
         __syncthreads();
         block_sort(keys, n2);
-        unsigned char* rec = reinterpret_cast<unsigned char*>(a.vp_records) + (size_t)row * vp_record_bytes(a.vp_k);
+        unsigned char* rec = reinterpret_cast<unsigned char*>(a.vp_records) +
+                             ((size_t)(kSplit ? blockIdx.y * gridDim.x : 0u) + row) * vp_record_bytes(a.vp_k);
         const uint32_t n_out = min(n_raw, a.vp_k);
         if (tid == 0) {
             float* hf = reinterpret_cast<float*>(rec);
@@ -1675,7 +1798,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 const unsigned long long key = keys[i];
                 const uint32_t ok = ~(uint32_t)(key >> 32);
                 o.x = __float_as_uint(key_to_float(ok));
-                o.y = (uint32_t)((int32_t)(uint32_t)(key & 0xffffffffull) + a.id_offset);
+                o.y = (uint32_t)((int32_t)(uint32_t)(key & 0xffffffffull) + id_off);
             }
             reinterpret_cast<uint2*>(rec + kVpHeaderBytes)[i] = o;
         }
@@ -1685,7 +1808,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     if (cfg.greedy) {
         // sampler.cpp:77-78, 88-91: first maximum of the row as handed over (bias and mask applied, no penalties)
         if (tid == 0) {
-            const int32_t t = (int32_t)arg_col + a.id_offset;
+            const int32_t t = (int32_t)arg_col + id_off;
             if (a.token) a.token[row] = t;
             if (a.prob) a.prob[row] = 1.0f;
             if (a.n_cand) a.n_cand[row] = 1;
@@ -1701,18 +1824,22 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
 
     // exact weights of the collected elements, min_p filter (sampler.cpp:33-35)
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
-    const uint32_t n_raw = min(s.ncand, a.scratch_cap);
-    bool overflow = s.ncand > a.scratch_cap;
+    const uint32_t n_raw = min(s.ncand, scratch_cap);
+    bool overflow = s.ncand > scratch_cap;
     double total_need = 0.0, band_need = 0.0; // need_sum: the row total that top_p scales, and its margin
     if (!s.nan0) {
         // Elements collected while the running maximum was still low are dropped by the final bound first.
         float thr_final = fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key));
+        // A long list under top_p alone: the bound is raised first, and the elements it leaves out get approximate
+        // weights (they join the part of the row total that carries the 1e-5 margin); exact weights only above it.
+        bool approx_below = false;
         if (cfg.need_sum && n_raw > 4096u) {
-            mass_cut(s, reinterpret_cast<float*>(dyn + kOffFinBitmap), scratch, n_raw, thr_final, m, cfg.inv_t, cfg.top_p,
-                     total_approx);
+            mass_cut(s, dyn, scratch, n_raw, thr_final, m, cfg.inv_t, cfg.top_p, total_approx);
             thr_final = fmaxf(thr_final, key_to_float(s.thr_topk_key));
+            approx_below = true;
         }
-        double exact = 0.0;
+        double below = 0.0, exact = 0.0;
+        const float c2w = cfg.inv_t * 1.4426950408889634f;
         for (uint32_t i0 = tid; i0 < n_raw; i0 += 4u * kThreads) {
             uint2 cv[4]; // four loads in flight
 #pragma unroll
@@ -1726,6 +1853,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 const bool in = __uint_as_float(c.x) >= thr_final;
                 if (!in && (!cfg.need_sum || i0 + (uint32_t)k * kThreads >= n_raw))
                     continue;
+                if (!in && approx_below) {
+                    below += (double)ex2_approx((__uint_as_float(c.x) - m) * c2w);
+                    continue;
+                }
                 const float x = __fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t);
                 const float q = expf_host_exact(x);
                 if (q == q)
@@ -1743,14 +1874,22 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             // rounding of a double sum taken in another order than the reference's.
             __syncthreads();
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
+            for (int o = 16; o > 0; o >>= 1) {
                 exact += __shfl_xor_sync(0xffffffffu, exact, o);
+                below += __shfl_xor_sync(0xffffffffu, below, o);
+            }
             if (lane == 0)
                 s.warp_sum[warp] = exact;
             __syncthreads();
             double sum = 0.0;
             for (int i = 0; i < kThreads / 32; ++i)
                 sum += s.warp_sum[i];
+            __syncthreads();
+            if (lane == 0)
+                s.warp_sum[warp] = below;
+            __syncthreads();
+            for (int i = 0; i < kThreads / 32; ++i)
+                total_approx += s.warp_sum[i];
             total_need = sum + total_approx;
             band_need = 1e-5 * total_approx + 0x1p-40 * total_need;
         }
@@ -1764,7 +1903,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     }
     if (!overflow && n > (uint32_t)kSortCap && !cfg.use_topp && !(cfg.top_k > 0 && cfg.top_k < n)) {
         const RowOut o = {a.token, a.prob, a.flags, a.n_cand, a.accepted, a.total_out, a.cand_ids, a.cand_q,
-                          a.cand_cap, a.id_offset, a.timing, mode};
+                          a.cand_cap, id_off, a.timing, mode};
         wide_id_ordered(s, reinterpret_cast<float*>(dyn + kOffKeys), scratch, qrow, n_raw, n, V,
                         fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key)), m, cfg.inv_t, cfg.minp_eff, row,
                         flags, u_row, u2_row, draft_row, o);
@@ -1777,11 +1916,20 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
         // returned above): a flat row under top_p, or a very large top_k. The candidates are sorted in global
         // memory — 8192-key runs in shared memory, then merge passes between the two halves of the row's scratch —
         // and the steps below read the list from there.
-        const unsigned long long* P = long_sort(s, keys, scratch, a.scratch_cap, n_raw, n,
+        const unsigned long long* P = long_sort(s, keys, scratch, scratch_cap, n_raw, n,
                                                 fmaxf(keep_threshold(cfg, m), key_to_float(s.thr_topk_key)), m, cfg.inv_t,
                                                 cfg.minp_eff);
         ksrc = P;
         pre_sorted = true;
+        // The float total and the walk below are sequential chains that take 32 candidates per step: fed from global
+        // memory they run at the pace of its latency, so a list that fits is staged in shared memory first.
+        if (n <= kDynBytes / 8u) {
+            unsigned long long* const staged = reinterpret_cast<unsigned long long*>(dyn);
+            for (uint32_t i = tid; i < n; i += kThreads)
+                staged[i] = P[i];
+            __syncthreads();
+            ksrc = staged;
+        }
     }
     if (!pre_sorted && n > (uint32_t)kSortCap)
         overflow = true;
@@ -1961,15 +2109,23 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             col_next = 0xffffffffu;
             if (base + 32u + lane < n)
                 fetch(base + 32u + lane, q_next, col_next);
-            const uint32_t dm = __ballot_sync(full, draft >= 0 && base + lane < n && (int32_t)col + a.id_offset == draft);
+            const uint32_t dm = __ballot_sync(full, draft >= 0 && base + lane < n && (int32_t)col + id_off == draft);
             if (dm) {
                 q_draft = __shfl_sync(full, q, __ffs(dm) - 1);
                 draft_idx = base + (uint32_t)__ffs(dm) - 1u;
             }
             const int cnt = (int)min(32u, n - base);
+            if (cnt == 32) {
+                // a full step unrolled whole: the 32 shuffles do not depend on the sum, so they all issue ahead of
+                // the chain of additions, which then runs at the adder's latency
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    total = __fadd_rn(total, __shfl_sync(full, q, j));
+            } else {
 #pragma unroll 8
-            for (int j = 0; j < cnt; ++j)
-                total = __fadd_rn(total, __shfl_sync(full, q, j));
+                for (int j = 0; j < cnt; ++j)
+                    total = __fadd_rn(total, __shfl_sync(full, q, j));
+            }
         }
         int32_t tok = -1, acc = 0;
         float prob = 0.0f;
@@ -1977,7 +2133,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             float q0;
             uint32_t c0;
             fetch(0, q0, c0);
-            tok = (int32_t)c0 + a.id_offset;
+            tok = (int32_t)c0 + id_off;
             prob = __fdiv_rn(q0, total);
         } else {
             uint32_t skip_idx = 0xffffffffu;
@@ -2009,30 +2165,54 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                     const float q = qn; // the skipped draft has weight 0: it never wins and changes nothing
                     qn = (base + 32u + lane < n && base + 32u + lane != skip_idx) ? q_of(base + 32u + lane) : 0.0f;
                     const int cnt = (int)min(32u, n - base);
-#pragma unroll 8
-                    for (int j = 0; j < cnt; ++j) {
-                        const float qj = __shfl_sync(full, q, j);
-                        if (!found && r < qj) {
-                            found = true;
-                            hit = base + (uint32_t)j;
-                            r_hit = r;
-                            q_hit = qj;
+                    if (cnt == 32) {
+                        // a full step: the chain of subtractions alone, noting which candidates the draw fell short
+                        // of; the first of them is the hit, and the remainder in front of it is subtracted again
+                        uint32_t short_of = 0u;
+                        float rr = r;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float qj = __shfl_sync(full, q, j);
+                            short_of |= (rr < qj) ? (1u << j) : 0u;
+                            rr = __fsub_rn(rr, qj);
                         }
-                        r = __fsub_rn(r, qj);
+                        if (short_of) {
+                            const int jh = __ffs((int)short_of) - 1;
+                            for (int j = 0; j < jh; ++j)
+                                r = __fsub_rn(r, __shfl_sync(full, q, j));
+                            found = true;
+                            hit = base + (uint32_t)jh;
+                            r_hit = r;
+                            q_hit = __shfl_sync(full, q, jh);
+                        } else {
+                            r = rr;
+                        }
+                    } else {
+#pragma unroll 8
+                        for (int j = 0; j < cnt; ++j) {
+                            const float qj = __shfl_sync(full, q, j);
+                            if (!found && r < qj) {
+                                found = true;
+                                hit = base + (uint32_t)j;
+                                r_hit = r;
+                                q_hit = qj;
+                            }
+                            r = __fsub_rn(r, qj);
+                        }
                     }
                 }
                 float qx;
                 uint32_t cx;
                 if (found) {
                     fetch(hit, qx, cx);
-                    tok = (int32_t)cx + a.id_offset;
+                    tok = (int32_t)cx + id_off;
                     prob = __fdiv_rn(q_hit, walk_total);
                     // boundary below (not for the first candidate) or above (not for the last)
                     if ((hit != first_valid && r_hit < eps) || (hit < last_valid && __fsub_rn(q_hit, r_hit) < eps))
                         flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
                 } else { // rounding: the last candidate (sampler.cpp:72)
                     fetch(last_valid, qx, cx);
-                    tok = (int32_t)cx + a.id_offset;
+                    tok = (int32_t)cx + id_off;
                     prob = __fdiv_rn(qx, walk_total);
                 }
             }
@@ -2058,7 +2238,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             float q;
             uint32_t col;
             fetch(i, q, col);
-            if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)col + a.id_offset;
+            if (a.cand_ids) a.cand_ids[(size_t)row * a.cand_cap + i] = (int32_t)col + id_off;
             if (a.cand_q) a.cand_q[(size_t)row * a.cand_cap + i] = q;
         }
     }
@@ -2077,10 +2257,13 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     if (e != cudaSuccess)
         return e;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(row_pipeline_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        e = cudaFuncSetAttribute(row_pipeline_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess)
             return e;
-        e = cudaFuncSetAttribute(row_pipeline_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        e = cudaFuncSetAttribute(row_pipeline_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e != cudaSuccess)
+            return e;
+        e = cudaFuncSetAttribute(row_pipeline_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess)
             return e;
         configured[dev] = true;
@@ -2102,8 +2285,12 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     RowKernelArgs first = a;
     first.pass = 0;
     const bool spec = a.spec_n_pos != 0u;
-    e = spec ? cudaLaunchKernelEx(&lc, row_pipeline_kernel<true>, first)
-             : cudaLaunchKernelEx(&lc, row_pipeline_kernel<false>, first);
+    if (a.split_w != 0u) { // shard records of every row, one CTA per (row, column shard)
+        lc.gridDim = dim3(batch, (a.n_vocab + a.split_w - 1u) / a.split_w);
+        return cudaLaunchKernelEx(&lc, row_pipeline_kernel<false, true>, first);
+    }
+    e = spec ? cudaLaunchKernelEx(&lc, row_pipeline_kernel<true, false>, first)
+             : cudaLaunchKernelEx(&lc, row_pipeline_kernel<false, false>, first);
     if (e != cudaSuccess)
         return e;
     // top_p alone (make_cfg: need_sum): rows whose nucleus the first launch could not settle are streamed again
@@ -2115,8 +2302,8 @@ cudaError_t launch_row_kernel(const RowKernelArgs& a, uint32_t batch, cudaStream
     if (a.mode != kModeVpLocal && kNucleusGuess < a.n_vocab && (a.params_dev || host_need_sum)) {
         RowKernelArgs second = a;
         second.pass = 1;
-        e = spec ? cudaLaunchKernelEx(&lc, row_pipeline_kernel<true>, second)
-                 : cudaLaunchKernelEx(&lc, row_pipeline_kernel<false>, second);
+        e = spec ? cudaLaunchKernelEx(&lc, row_pipeline_kernel<true, false>, second)
+                 : cudaLaunchKernelEx(&lc, row_pipeline_kernel<false, false>, second);
     }
     return e;
 }

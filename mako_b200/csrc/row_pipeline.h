@@ -59,6 +59,12 @@ struct RowKernelArgs {
     uint32_t spec_n_pos;
     const int32_t* spec_drafts; // [n_seq][spec_n_pos - 1]
     const int32_t* spec_forced; // [n_seq][spec_n_pos] forced token or -1, or NULL
+    // split launch (shard records only): every row's columns in shards of split_w columns, one CTA per (row, shard);
+    // records laid out [n_shards][batch]. 0: off
+    uint32_t split_w;
+    // follow-up launch: only rows whose flags (written by an earlier step) have one of these bits set are processed
+    const uint32_t* only_flagged;
+    uint32_t only_flagged_mask;
     uint32_t debug_skip_tile;   // test hook: the copy of this tile is never requested (0xffffffff: none)
     uint32_t debug_wait_probes; // test hook: probes a wait for a tile makes before it gives up (0: the default)
 };

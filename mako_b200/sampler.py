@@ -127,6 +127,11 @@ class BatchSampler:
         before the wait (the caller promises that the previous kernel writes no parameters, histories or biases)."""
         check(lib.mk_sampler_set_overlap(self._h, int(mode)))
 
+    def set_split(self, on: bool) -> None:
+        """Whether a small batch (at most 8 rows, shared parameters, drawing under a top_k of at most 64) has every
+        row split over many CTAs and merged (the default) or runs as one CTA per row (mk_sampler_set_split)."""
+        check(lib.mk_sampler_set_split(self._h, 1 if on else 0))
+
     # -- argument marshalling -----------------------------------------------------------------------------------
     def _rows(self, logits: torch.Tensor, params, history=None, history_len=None, mask=None, bias=None,
               n_vocab=None, id_offset: int = 0) -> RowsC:

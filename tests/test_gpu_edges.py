@@ -261,3 +261,22 @@ def test_a_wait_that_runs_out_ends_the_row_in_good_order(ref, with_history):
     torch.cuda.synchronize()
     want = [ref.sample(p, inp.logits[r], inp.u[r], **inp.row_kwargs(r))["token"] for r in range(b)]
     assert res.token.cpu().tolist() == want
+
+
+def test_top_k_alone_keeps_the_reference_candidate_set(gpu_sampler_factory, ref):
+    """top_k without top_p is the one case where the draw ORDER is not the reference's (it walks whatever order
+    std::nth_element left, sampler.cpp:41, 64-73; here and in the checker the list is sorted). What must still be
+    identical is the candidate set with its weights: ids and weights are compared as sets, order ignored."""
+    v, b = 50257, 6
+    inp = Inputs(515, b, v, n_history=300)
+    for p in (SamplingParams(temperature=1.0, top_k=50), SamplingParams(temperature=0.7, top_k=5, min_p=0.001,
+                                                                       repetition_penalty=1.2)):
+        res = gpu_rows(gpu_sampler_factory, inp.logits, p, inp.u, cap=64, history=inp.history)
+        ids, qs, n = res.cand_ids.cpu().numpy(), res.cand_q.cpu().numpy(), res.n_cand.cpu().numpy()
+        flags = res.flags.cpu().numpy()
+        for r in range(b):
+            w = ref.sample(p, inp.logits[r], inp.u[r], cap=64, history=inp.history[r])
+            assert not (flags[r] & 0x52) and n[r] == w["n_cand"] == p.top_k
+            got = sorted(zip(ids[r, :n[r]].tolist(), qs[r, :n[r]].view(np.uint32).tolist()))
+            want = sorted(zip(w["cand_ids"].tolist(), w["cand_q"].view(np.uint32).tolist()))
+            assert got == want, f"row {r}"
