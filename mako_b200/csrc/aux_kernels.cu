@@ -548,7 +548,7 @@ cudaError_t launch_rank_force(const float* logits, uint64_t ld, uint32_t batch, 
 constexpr int kPickThreads = 256, kPickMaxSeq = 8, kPickMaxRank = 256;
 
 template <int kSeq> // sequences the launch can carry: 1 (the reference's case, fewer registers) or kPickMaxSeq
-__global__ void __launch_bounds__(kPickThreads, kSeq == 1 ? 4 : 3) draft_score_kernel(const float* logits, uint64_t ld, const float* head,
+__global__ void __launch_bounds__(kPickThreads, kSeq == 1 ? 4 : 2) draft_score_kernel(const float* logits, uint64_t ld, const float* head,
                                                                   const float* embed, const int32_t* prev,
                                                                   uint32_t n_seq, uint32_t n_vocab, uint32_t rank,
                                                                   uint32_t n_embed, unsigned long long* best,
@@ -624,17 +624,15 @@ __global__ void __launch_bounds__(kPickThreads, kSeq == 1 ? 4 : 3) draft_score_k
             for (int q = 0; q < kSeq; ++q) {
                 const float4 e0 = *reinterpret_cast<const float4*>(&s_e[q][4u * lane]);
                 const float4 e1 = *reinterpret_cast<const float4*>(&s_e[q][4u * lane + 128u]);
+                // two lanes of the product per instruction (even and odd elements apart, added at the end): the kernel
+                // is bound by the issue of its multiply-adds, not by memory
 #pragma unroll
                 for (uint32_t r = 0; r < kRows; ++r) {
-                    float t = h[r][0].x * e0.x;
-                    t = fmaf(h[r][0].y, e0.y, t);
-                    t = fmaf(h[r][0].z, e0.z, t);
-                    t = fmaf(h[r][0].w, e0.w, t);
-                    t = fmaf(h[r][1].x, e1.x, t);
-                    t = fmaf(h[r][1].y, e1.y, t);
-                    t = fmaf(h[r][1].z, e1.z, t);
-                    t = fmaf(h[r][1].w, e1.w, t);
-                    acc[q * 4 + (int)r] = t;
+                    float2 t = mul2(make_float2(h[r][0].x, h[r][0].y), make_float2(e0.x, e0.y));
+                    t = fma2(make_float2(h[r][0].z, h[r][0].w), make_float2(e0.z, e0.w), t);
+                    t = fma2(make_float2(h[r][1].x, h[r][1].y), make_float2(e1.x, e1.y), t);
+                    t = fma2(make_float2(h[r][1].z, h[r][1].w), make_float2(e1.z, e1.w), t);
+                    acc[q * 4 + (int)r] = t.x + t.y;
                 }
             }
 #pragma unroll
@@ -718,7 +716,8 @@ cudaError_t launch_draft_pick(const float* logits, uint64_t ld, const float* hea
     // `best` (the maxima, then the ticket counter) is zero on entry: the handle clears it once and the kernel's last
     // CTA clears what it has read
     const uint32_t rows_per_trip = (kPickThreads / 32) * 4;
-    const uint32_t grid = min((n_vocab + rows_per_trip - 1) / rows_per_trip, 148u * 4u); // persistent, grid-stride
+    // persistent, grid-stride: as many CTAs as stay resident (four per SM for one sequence, two for several)
+    const uint32_t grid = min((n_vocab + rows_per_trip - 1) / rows_per_trip, 148u * (n_seq == 1 ? 4u : 2u));
     if (n_seq == 1)
         draft_score_kernel<1><<<grid, kPickThreads, 0, stream>>>(logits, ld, head, embed, prev, n_seq, n_vocab, rank,
                                                                 n_embed, best, x, x_ld, w, dim, draft, conf);
