@@ -819,6 +819,173 @@ __device__ __noinline__ const unsigned long long* long_sort(Smem& s, unsigned lo
     return P;
 }
 
+constexpr uint32_t kWideCand = 64;
+// The one-warp finish of row_pipeline_kernel for 33 to 64 candidates (a top_k of 40 or 50): the same steps with two
+// candidates a lane — a 64-key network, its last level between a lane's own two keys — and chains that take candidate
+// j from register j / 32 of lane j % 32 (sampler.cpp:39-73, 86-107). Called by warp 0 with the candidates' (weight,
+// column) pairs in `fkeys`. Out of line: the rows it does not serve run the code they always ran.
+__device__ __noinline__ void wide_finish(Smem& s, const unsigned long long* fkeys, uint32_t n, uint32_t top_k, bool use_topp,
+                                         float top_p, float inv_t, float m, uint32_t flags, int32_t draft_row, float u_row,
+                                         float u2_row, uint32_t row, RowOut o)
+{
+        const uint32_t full = 0xffffffffu, lane = threadIdx.x & 31u;
+    const int mode = o.mode;
+    const int32_t id_off = o.id_offset;
+            uint32_t fl = flags;
+        const bool cut_k = top_k > 0 && top_k < n; // sampler.cpp:39
+        const bool sorted = cut_k || use_topp;         // else ascending id
+        unsigned long long key[2];
+#pragma unroll
+        for (uint32_t r = 0; r < 2; ++r) {
+            key[r] = ~0ull;
+            if (r * 32u + lane < n) {
+                const unsigned long long raw = fkeys[r * 32u + lane];
+                const float q = __uint_as_float((uint32_t)(raw >> 32));
+                const uint32_t col = (uint32_t)(raw & 0xffffffffull);
+                key[r] = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
+            }
+        }
+        for (uint32_t k = 2; k <= 64u; k <<= 1)
+            for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+                if (j == 32u) { // k == 64: element `lane` against element `lane + 32`, ascending
+                    const unsigned long long lo = min(key[0], key[1]), hi = max(key[0], key[1]);
+                    key[0] = lo;
+                    key[1] = hi;
+                } else {
+#pragma unroll
+                    for (uint32_t r = 0; r < 2; ++r) {
+                        const uint32_t i = r * 32u + lane;
+                        const unsigned long long other = __shfl_xor_sync(full, key[r], j);
+                        const bool keep_small = ((i & j) == 0) == ((i & k) == 0);
+                        key[r] = (keep_small == (key[r] < other)) ? key[r] : other;
+                    }
+                }
+            }
+        float q[2];
+        uint32_t col[2];
+#pragma unroll
+        for (uint32_t r = 0; r < 2; ++r) {
+            if (sorted) {
+                q[r] = __uint_as_float(~(uint32_t)(key[r] >> 32));
+                col[r] = (uint32_t)(key[r] & 0xffffffffull);
+            } else {
+                q[r] = __uint_as_float((uint32_t)(key[r] & 0xffffffffull));
+                col[r] = (uint32_t)(key[r] >> 32);
+            }
+            if (r * 32u + lane >= n)
+                q[r] = 0.0f;
+        }
+        auto q_at = [&](uint32_t j) -> float { return __shfl_sync(full, j < 32u ? q[0] : q[1], (int)(j & 31u)); };
+        auto col_at = [&](uint32_t j) -> uint32_t { return __shfl_sync(full, j < 32u ? col[0] : col[1], (int)(j & 31u)); };
+        if (cut_k) { // sampler.cpp:40-42; the tie rule is the general finish's
+            const float qk = q_at(top_k - 1u);
+            const uint32_t edge_key = s.thr_topk_key;
+            const float below = key_to_float(edge_key - 1u);
+            if (edge_key > order_key(-FLT_MAX) && expf_host_exact(__fmul_rn(__fsub_rn(below, m), inv_t)) >= qk)
+                fl |= MK_FLAG_GUARD_BAND;
+            n = top_k;
+        }
+        if (use_topp) { // sampler.cpp:44-61, sequentially
+            double total_d = 0.0;
+            for (uint32_t j = 0; j < n; ++j)
+                total_d += (double)q_at(j);
+            const double band = 0x1p-40 * total_d, want = (double)top_p * total_d;
+            double run = 0.0, prev = 0.0;
+            uint32_t k = 0;
+            for (uint32_t j = 0; j < n && run < want; ++j) {
+                prev = run;
+                run += (double)q_at(j);
+                k = j + 1u;
+            }
+            if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
+                fl |= MK_FLAG_GUARD_BAND;
+            n = max(k, 1u);
+        }
+#pragma unroll
+        for (uint32_t r = 0; r < 2; ++r)
+            if (r * 32u + lane >= n)
+                q[r] = 0.0f;
+        float total = 0.0f;
+        for (uint32_t j = 0; j < n; ++j)
+            total = __fadd_rn(total, q_at(j));
+        const int32_t draft = (mode == kModeVerify) ? draft_row : -1;
+        const uint32_t dm0 = __ballot_sync(full, draft >= 0 && lane < n && (int32_t)col[0] + id_off == draft);
+        const uint32_t dm1 = __ballot_sync(full, draft >= 0 && 32u + lane < n && (int32_t)col[1] + id_off == draft);
+        const uint32_t draft_idx = dm0 ? (uint32_t)__ffs((int)dm0) - 1u : (dm1 ? 31u + (uint32_t)__ffs((int)dm1) : 0xffffffffu);
+        const float q_draft = (dm0 | dm1) ? q_at(draft_idx) : 0.0f;
+        int32_t tok = -1, acc = 0;
+        float prob = 0.0f;
+        if (mode == kModeDistOnly) {
+            tok = (int32_t)col_at(0) + id_off;
+            prob = __fdiv_rn(q_at(0), total);
+        } else {
+            uint32_t skip_idx = 0xffffffffu;
+            float walk_total = total;
+            if (mode == kModeVerify) { // sampler.cpp:100-106
+                acc = __fmul_rn(u_row, total) < q_draft;
+                if (acc) {
+                    tok = draft;
+                    prob = __fdiv_rn(q_draft, total);
+                } else {
+                    skip_idx = draft_idx;
+                    walk_total = __fsub_rn(total, q_draft);
+                    if (n == 1 && draft_idx == 0u) { // nothing but the rejected draft
+                        tok = draft;
+                        prob = 1.0f;
+                    }
+                }
+            }
+            if (tok < 0) {
+                float r = __fmul_rn((mode == kModeVerify) ? u2_row : u_row, walk_total);
+                const float eps = 1e-6f * walk_total;
+                const uint32_t first_valid = (skip_idx == 0u) ? 1u : 0u;
+                const uint32_t last_valid = (skip_idx == n - 1u) ? n - 2u : n - 1u;
+                if (lane == skip_idx)
+                    q[0] = 0.0f; // the skipped draft never wins
+                if (32u + lane == skip_idx)
+                    q[1] = 0.0f;
+                uint32_t hit = last_valid; // rounding: the last candidate (sampler.cpp:72)
+                float q_hit = q_at(last_valid);
+                bool found = false;
+                for (uint32_t j = 0; j < n && !found; ++j) {
+                    const float qj = q_at(j);
+                    if (r < qj) {
+                        found = true;
+                        hit = j;
+                        q_hit = qj;
+                        // boundary below (not for the first candidate) or above (not for the last)
+                        if ((j != first_valid && r < eps) || (j < last_valid && __fsub_rn(qj, r) < eps))
+                            fl |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                    } else {
+                        r = __fsub_rn(r, qj);
+                    }
+                }
+                tok = (int32_t)col_at(hit) + id_off;
+                prob = __fdiv_rn(q_hit, walk_total);
+            }
+        }
+        if (lane == 0) {
+            if (o.token) o.token[row] = tok;
+            if (o.prob) o.prob[row] = prob;
+            if (o.flags) o.flags[row] = fl;
+            if (o.n_cand) o.n_cand[row] = n;
+            if (o.accepted) o.accepted[row] = acc;
+            if (o.total_out) o.total_out[row] = total;
+            if (o.timing)
+                o.timing[(size_t)row * 64 + 3] = global_ns();
+        }
+        // the candidate list as the chains saw it, except that a rejected draft keeps its weight there
+#pragma unroll
+        for (uint32_t r = 0; r < 2; ++r) {
+            const uint32_t i = r * 32u + lane;
+            if (i < min(n, o.cand_cap)) {
+                const float qo = sorted ? __uint_as_float(~(uint32_t)(key[r] >> 32)) : __uint_as_float((uint32_t)(key[r] & 0xffffffffull));
+                if (o.cand_ids) o.cand_ids[(size_t)row * o.cand_cap + i] = (int32_t)col[r] + id_off;
+                if (o.cand_q) o.cand_q[(size_t)row * o.cand_cap + i] = qo;
+            }
+        }
+    }
+
 } // namespace
 
 // kSpec: the rows of a speculative round (row = sequence * n_pos + position); compiled apart, so that the plain
@@ -1550,7 +1717,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
     // is short and contiguous; every other row falls through to the general finish below, which recomputes from the
     // collected elements.
     constexpr uint32_t kFastRaw = 256;
-    if (mode != kModeVpLocal && !cfg.greedy && !s.nan0 && s.ncand <= kFastRaw && s.ncand <= scratch_cap) {
+    if (mode != kModeVpLocal && !cfg.greedy && !s.nan0 && s.ncand <= 2u * kFastRaw && s.ncand <= scratch_cap) {
         // Compiled twice: rows whose total is the candidates' own (nearly all) run code that knows nothing of the
         // row total of top_p alone.
         auto short_finish = [&](auto row_total_tag) {
@@ -1561,32 +1728,41 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
             unsigned long long* const fkeys = reinterpret_cast<unsigned long long*>(dyn + kOffKeys);
             uint32_t n = 0;
             double sum_kept = 0.0, sum_rest = 0.0; // top_p alone: exact weights at or above the bound, the others
-            uint2 craw[kFastRaw / 32]; // all requested at once: one trip to memory under load, not one per chunk
+            for (uint32_t r0 = 0; r0 < n_raw && n <= kWideCand; r0 += kFastRaw) { // once, for nearly every row
+                uint2 craw[kFastRaw / 32]; // all requested at once: one trip to memory under load, not one per chunk
 #pragma unroll
-            for (uint32_t i = 0; i < kFastRaw / 32; ++i)
-                craw[i] = (i * 32u + lane < n_raw) ? scratch[i * 32u + lane] : make_uint2(0xff800000u, 0u);
+                for (uint32_t i = 0; i < kFastRaw / 32; ++i)
+                    craw[i] = (r0 + i * 32u + lane < n_raw) ? scratch[r0 + i * 32u + lane] : make_uint2(0xff800000u, 0u);
 #pragma unroll
-            for (uint32_t i = 0; i < kFastRaw / 32; ++i) {
-                if (i * 32u >= n_raw || n > 32u)
-                    break;
-                const uint2 c = craw[i];
-                float q = 0.0f;
-                if (__uint_as_float(c.x) >= thr_final) {
-                    q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
-                    if (kRowTotal && q == q)
-                        sum_kept += (double)q;
-                } else if (kRowTotal) {
-                    // collected while the bound was lower: part of the row total, never a candidate
-                    sum_rest += (double)ex2_approx((__uint_as_float(c.x) - m) * (cfg.inv_t * 1.4426950408889634f));
+                for (uint32_t i = 0; i < kFastRaw / 32; ++i) {
+                    if (r0 + i * 32u >= n_raw || n > kWideCand)
+                        break;
+                    const uint2 c = craw[i];
+                    float q = 0.0f;
+                    if (__uint_as_float(c.x) >= thr_final) {
+                        q = expf_host_exact(__fmul_rn(__fsub_rn(__uint_as_float(c.x), m), cfg.inv_t));
+                        if (kRowTotal && q == q)
+                            sum_kept += (double)q;
+                    } else if (kRowTotal) {
+                        // collected while the bound was lower: part of the row total, never a candidate
+                        sum_rest += (double)ex2_approx((__uint_as_float(c.x) - m) * (cfg.inv_t * 1.4426950408889634f));
+                    }
+                    const bool ok = q >= cfg.minp_eff && q > 0.0f; // false for NaN
+                    const uint32_t bal = __ballot_sync(full, ok);
+                    const uint32_t pos = n + (uint32_t)__popc(bal & ((1u << lane) - 1u));
+                    if (ok && pos < kWideCand)
+                        fkeys[pos] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
+                    n += (uint32_t)__popc(bal);
                 }
-                const bool ok = q >= cfg.minp_eff && q > 0.0f; // false for NaN
-                const uint32_t bal = __ballot_sync(full, ok);
-                const uint32_t pos = n + (uint32_t)__popc(bal & ((1u << lane) - 1u));
-                if (ok && pos < 32u)
-                    fkeys[pos] = ((unsigned long long)__float_as_uint(q) << 32) | c.y;
-                n += (uint32_t)__popc(bal);
             }
             __syncwarp();
+            bool done = n <= 32u;
+            if (!kRowTotal && n > 32u && n <= kWideCand) {
+                const RowOut o = {a.token, a.prob, a.flags, a.n_cand, a.accepted, a.total_out, a.cand_ids, a.cand_q,
+                                  a.cand_cap, id_off, a.timing, mode};
+                wide_finish(s, fkeys, n, cfg.top_k, cfg.use_topp, cfg.top_p, cfg.inv_t, m, flags, draft_row, u_row, u2_row, row, o);
+                done = true;
+            }
             if (n <= 32u) {
                 uint32_t fl = flags;
                 bool retry = false;
@@ -1743,7 +1919,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_pipeline_kernel(const RowKern
                 }
             }
             if (lane == 0)
-                s.n_final = (n <= 32u) ? 1u : 0u; // 1: the row is done
+                s.n_final = done ? 1u : 0u; // 1: the row is done
         };
         if (warp == 0) {
             if (cfg.need_sum)

@@ -280,3 +280,42 @@ def test_top_k_alone_keeps_the_reference_candidate_set(gpu_sampler_factory, ref)
             got = sorted(zip(ids[r, :n[r]].tolist(), qs[r, :n[r]].view(np.uint32).tolist()))
             want = sorted(zip(w["cand_ids"].tolist(), w["cand_q"].view(np.uint32).tolist()))
             assert got == want, f"row {r}"
+
+
+@pytest.mark.parametrize("params", [
+    SamplingParams(temperature=1.0, top_k=50),
+    SamplingParams(temperature=0.9, top_k=45, top_p=0.98),
+    SamplingParams(temperature=1.2, top_k=33, min_p=0.001, repetition_penalty=1.2, presence_penalty=0.3,
+                   frequency_penalty=0.1),
+    SamplingParams(temperature=1.5, min_p=0.3),
+], ids=["top_k50", "top_k45_top_p", "top_k33_penalised", "min_p_about_50"])
+def test_rows_with_33_to_64_candidates(gpu_sampler_factory, ref, params):
+    """Between 33 and 64 candidates a row is finished by one warp with two candidates a lane: token, probability,
+    candidate list and weights against the reference for sampling, token and acceptance for verification (drafts that
+    are the likeliest token, a token in the second half of the list, and a token outside it)."""
+    import torch
+    from helpers import Inputs, compare_sample, oracle_sample_rows
+    v, b = 129280, 48
+    # no spikes: the largest logits of a row lie close together, so min_p 0.3 at T 1.5 keeps some tens of them
+    inp = Inputs(8100, b, v, n_history=256, n_spikes=0)
+    g = inp.to_gpu()
+    s = gpu_sampler_factory(v, b, 64)
+    s.set_split(False)
+    res = s.sample(g["logits"], params, g["u"], **g["kw"])
+    torch.cuda.synchronize()
+    want = oracle_sample_rows(ref, params, inp, cap=64)
+    compare_sample(res, want, cap=64)
+    n_c = np.array([w["n_cand"] for w in want])
+    if params.top_p >= 1.0: # what is left after top_p says nothing about how many candidates went in
+        assert ((n_c > 32) & (n_c <= 64)).sum() >= 4, "the inputs must land in the two-per-lane finish"
+    draft = np.zeros(b, dtype=np.int32)
+    for i in range(b):
+        ids = want[i]["cand_ids"]
+        draft[i] = ids[0] if i % 3 == 0 else (ids[min(len(ids) - 1, 40)] if i % 3 == 1 else (i * 977) % v)
+    res = s.verify(g["logits"], params, torch.from_numpy(draft).cuda(), g["u"], g["u2"], **g["kw"])
+    torch.cuda.synchronize()
+    tok, acc = res.token.cpu().numpy(), res.accepted.cpu().numpy()
+    for i in range(b):
+        wt, wa = ref.verify(params, inp.logits[i], int(draft[i]), inp.u[i], inp.u2[i], **inp.row_kwargs(i))
+        assert (tok[i], bool(acc[i])) == (wt, wa), f"row {i}"
+    s.set_split(True)
