@@ -273,7 +273,7 @@ cudaError_t launch_vp_merge(const VpMergeArgs& a, cudaStream_t stream)
 // their float totals; draft_token was drawn from q. Accept iff u_accept * q(d) < p(d) on normalised probabilities;
 // otherwise walk max(0, p - q) over the union in ascending id with u_resample.
 namespace {
-constexpr int kPqThreads = 128;
+constexpr int kPqThreads = 512; // the sort of two long lists (a flat row: thousands of candidates each) is what takes the time
 }
 
 __global__ void __launch_bounds__(kPqThreads) pq_resolve_kernel(const PqResolveArgs a)
