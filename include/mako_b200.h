@@ -268,7 +268,8 @@ int mk_sampler_sample_host(mk_sampler* s, const mk_rows* host_rows, const float*
  * (src/gen/sampler.hpp:22-45) call for call. Keeps the parameters, the generated-token history (accept,
  * sampler.cpp:15-18) and a std::mt19937_64 seeded like the reference's, from which it takes the same uniforms in
  * the same order: one per sample(), one per verify() plus one more after a rejection, none when greedy. With the
- * same seed the token stream is the reference's, with one exception: top_k active and top_p >= 1. There the reference
+ * same seed the token stream is the reference's, with one exception: top_k truncating (more candidates than top_k)
+ * and top_p >= 1. There the reference
  * walks its candidates in the order std::nth_element happened to leave them (sampler.cpp:41, 64-73), which no
  * specification fixes; this library walks them sorted by (weight descending, id ascending). The candidate set and
  * every probability are the same, the draw order is not, so the streams differ in that one case. `logits`

@@ -14,8 +14,9 @@
  *   reference sampler is handed. History ids are replayed through accept() (sampler.cpp:15-18).
  *   A caller-supplied uniform u in [0,1) replaces the reference's own generator draw: the reference computes
  *   r = uniform_real_distribution<float>(0,total)(rng) = u * total (sampler.cpp:66,100), here u is given.
- *   With top_k active and top_p >= 1 the reference's candidate order is whatever nth_element leaves
- *   (sampler.cpp:41); both checkers sort that case by (q descending, id ascending) before drawing.
+ *   With top_k active and top_p >= 1 the reference's candidate order, when top_k truncates, is whatever
+ *   nth_element leaves (sampler.cpp:41); both checkers sort that case by (q descending, id ascending) before
+ *   drawing. When no more than top_k candidates exist the list stays in ascending id, as in the reference.
  */
 #ifndef MAKO_ORACLE_API_H
 #define MAKO_ORACLE_API_H

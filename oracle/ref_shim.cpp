@@ -30,11 +30,23 @@ public:
     const std::vector<orc::Cand>& distribution(const float* logits)
     {
         s_.distribution(logits);
-        // top_k without top_p leaves nth_element's order (src/gen/sampler.cpp:41): canonical order is sorted.
-        if (top_k_only_)
-            std::sort(s_.cand_.begin(), s_.cand_.end(), [](const orc::Cand& a, const orc::Cand& b) {
-                return a.first > b.first || (a.first == b.first && a.second < b.second);
-            });
+        // top_k without top_p, when it truncates, leaves nth_element's order (src/gen/sampler.cpp:41): canonical order
+        // is sorted. When no more than top_k candidates exist nothing is reordered there (ascending id, :30-36) and
+        // nothing is here. A list of exactly top_k entries may be either: the candidates are counted again from the
+        // sampler's own edited logits, with its expressions (:29-35).
+        if (top_k_only_ && s_.cand_.size() == size_t(s_.p_.top_k)) {
+            const float inv_t = 1.0f / s_.p_.temperature, m = *std::max_element(s_.work_.begin(), s_.work_.end());
+            size_t n_before = 0;
+            for (const float l : s_.work_) {
+                const float q = std::exp((l - m) * inv_t);
+                if (q >= std::min(s_.p_.min_p, 1.0f) && q > 0.0f)
+                    ++n_before;
+            }
+            if (n_before > s_.cand_.size())
+                std::sort(s_.cand_.begin(), s_.cand_.end(), [](const orc::Cand& a, const orc::Cand& b) {
+                    return a.first > b.first || (a.first == b.first && a.second < b.second);
+                });
+        }
         return s_.cand_;
     }
     int32_t sample_own_rng(const float* logits) { return s_.sample(logits); }

@@ -118,6 +118,7 @@ def test_own_generator_path_equals_uniform_driven_path():
     SamplingParams(temperature=1.0),
     SamplingParams(temperature=0.6, top_p=0.95),
     SamplingParams(temperature=1.3, top_k=17),
+    SamplingParams(temperature=1.3, top_k=200, min_p=0.3),   # fewer candidates than top_k: nothing is reordered
     SamplingParams(temperature=0.0),
 ])
 def test_port_equals_reference(params):
@@ -160,3 +161,20 @@ def test_one_hot_drafter_reduces_to_verify(orc):
         assert dd == d and acc == acc2
         if acc:
             assert tok == tok2 == d
+
+
+@pytest.mark.skipif(not have_reference(), reason="reference build not present")
+def test_top_k_that_does_not_truncate_leaves_ascending_ids():
+    """top_k without top_p: the checker sorts the list only when top_k truncated it (the reference's own order there
+    is nth_element's); with no more candidates than top_k, and with exactly top_k, the list stays in ascending id as
+    the reference leaves it (sampler.cpp:30-43), and the draw walks it in that order."""
+    ref = Oracle("reference")
+    v = 5003
+    lg = np.full(v, -30.0, dtype=np.float32)
+    ids = np.array([4000, 17, 2500, 900, 3100], dtype=np.int64)
+    lg[ids] = np.array([1.0, 2.0, 3.0, 2.5, 0.5], dtype=np.float32)
+    for top_k, expect in ((9, sorted(ids.tolist())), (5, sorted(ids.tolist())), (3, [2500, 900, 17])):
+        p = SamplingParams(temperature=1.0, top_k=top_k, min_p=0.01)
+        r = ref.sample(p, lg, 0.999, cap=16)
+        assert r["cand_ids"].tolist() == expect, (top_k, r["cand_ids"])
+        assert r["token"] == expect[-1]       # u close to 1 lands on the last candidate of the walk
