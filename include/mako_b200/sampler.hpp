@@ -12,8 +12,9 @@
 // State, threading and generator follow the reference: one object per request, not thread-safe, a std::mt19937_64
 // seeded with `seed` that yields one uniform per sample(), one per verify() plus one more after a rejection, none
 // when greedy — so a session that swaps this class in draws the same tokens as before for the same seed. The one
-// exception is top_k truncating (more candidates than top_k) with top_p >= 1: the reference then walks its candidates in whatever order
-// std::nth_element left them (sampler.cpp:41, 64-73), this class in sorted order (weight descending, id ascending).
+// exception is top_k truncating (more candidates than top_k) with top_p >= 1: the reference then walks its candidates
+// in whatever order std::nth_element left them (sampler.cpp:41, 64-73), this class in sorted order (weight
+// descending, id ascending).
 // Candidate set and probabilities are identical; the seeded token stream is not.
 #pragma once
 
