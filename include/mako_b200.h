@@ -100,8 +100,10 @@ const char* mk_version(void);
 const char* mk_last_error(void);
 
 /* Replaces Sampler::Sampler(params, n_vocab, seed) (sampler.cpp:9-13) for a batch: allocates the handle's scratch
- * (candidate lists) for up to max_batch rows of at most n_vocab columns on `device`. n_vocab == 0 is
- * MK_ERR_INVALID_ARGUMENT, as the reference throws. Nothing is allocated after this call. */
+ * for up to max_batch rows of at most n_vocab columns on `device` — candidate lists of 16 * n_vocab bytes a row,
+ * twice (the two row sets of mk_sampler_verify_pq_batch run side by side), and 64 KB of candidate lists a row for
+ * that call's two distributions: about 5 MB a row at 151,552 columns. n_vocab == 0 is MK_ERR_INVALID_ARGUMENT, as the
+ * reference throws. Nothing is allocated after this call. */
 int mk_sampler_create(mk_sampler** out, int device, uint32_t n_vocab, uint32_t max_batch);
 void mk_sampler_destroy(mk_sampler* s);
 

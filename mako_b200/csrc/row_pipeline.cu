@@ -828,163 +828,163 @@ __device__ __noinline__ void wide_finish(Smem& s, const unsigned long long* fkey
                                          float top_p, float inv_t, float m, uint32_t flags, int32_t draft_row, float u_row,
                                          float u2_row, uint32_t row, RowOut o)
 {
-        const uint32_t full = 0xffffffffu, lane = threadIdx.x & 31u;
+    const uint32_t full = 0xffffffffu, lane = threadIdx.x & 31u;
     const int mode = o.mode;
     const int32_t id_off = o.id_offset;
-            uint32_t fl = flags;
-        const bool cut_k = top_k > 0 && top_k < n; // sampler.cpp:39
-        const bool sorted = cut_k || use_topp;         // else ascending id
-        unsigned long long key[2];
+    uint32_t fl = flags;
+    const bool cut_k = top_k > 0 && top_k < n; // sampler.cpp:39
+    const bool sorted = cut_k || use_topp;         // else ascending id
+    unsigned long long key[2];
 #pragma unroll
-        for (uint32_t r = 0; r < 2; ++r) {
-            key[r] = ~0ull;
-            if (r * 32u + lane < n) {
-                const unsigned long long raw = fkeys[r * 32u + lane];
-                const float q = __uint_as_float((uint32_t)(raw >> 32));
-                const uint32_t col = (uint32_t)(raw & 0xffffffffull);
-                key[r] = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
-            }
-        }
-        for (uint32_t k = 2; k <= 64u; k <<= 1)
-            for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-                if (j == 32u) { // k == 64: element `lane` against element `lane + 32`, ascending
-                    const unsigned long long lo = min(key[0], key[1]), hi = max(key[0], key[1]);
-                    key[0] = lo;
-                    key[1] = hi;
-                } else {
-#pragma unroll
-                    for (uint32_t r = 0; r < 2; ++r) {
-                        const uint32_t i = r * 32u + lane;
-                        const unsigned long long other = __shfl_xor_sync(full, key[r], j);
-                        const bool keep_small = ((i & j) == 0) == ((i & k) == 0);
-                        key[r] = (keep_small == (key[r] < other)) ? key[r] : other;
-                    }
-                }
-            }
-        float q[2];
-        uint32_t col[2];
-#pragma unroll
-        for (uint32_t r = 0; r < 2; ++r) {
-            if (sorted) {
-                q[r] = __uint_as_float(~(uint32_t)(key[r] >> 32));
-                col[r] = (uint32_t)(key[r] & 0xffffffffull);
-            } else {
-                q[r] = __uint_as_float((uint32_t)(key[r] & 0xffffffffull));
-                col[r] = (uint32_t)(key[r] >> 32);
-            }
-            if (r * 32u + lane >= n)
-                q[r] = 0.0f;
-        }
-        auto q_at = [&](uint32_t j) -> float { return __shfl_sync(full, j < 32u ? q[0] : q[1], (int)(j & 31u)); };
-        auto col_at = [&](uint32_t j) -> uint32_t { return __shfl_sync(full, j < 32u ? col[0] : col[1], (int)(j & 31u)); };
-        if (cut_k) { // sampler.cpp:40-42; the tie rule is the general finish's
-            const float qk = q_at(top_k - 1u);
-            const uint32_t edge_key = s.thr_topk_key;
-            const float below = key_to_float(edge_key - 1u);
-            if (edge_key > order_key(-FLT_MAX) && expf_host_exact(__fmul_rn(__fsub_rn(below, m), inv_t)) >= qk)
-                fl |= MK_FLAG_GUARD_BAND;
-            n = top_k;
-        }
-        if (use_topp) { // sampler.cpp:44-61, sequentially
-            double total_d = 0.0;
-            for (uint32_t j = 0; j < n; ++j)
-                total_d += (double)q_at(j);
-            const double band = 0x1p-40 * total_d, want = (double)top_p * total_d;
-            double run = 0.0, prev = 0.0;
-            uint32_t k = 0;
-            for (uint32_t j = 0; j < n && run < want; ++j) {
-                prev = run;
-                run += (double)q_at(j);
-                k = j + 1u;
-            }
-            if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
-                fl |= MK_FLAG_GUARD_BAND;
-            n = max(k, 1u);
-        }
-#pragma unroll
-        for (uint32_t r = 0; r < 2; ++r)
-            if (r * 32u + lane >= n)
-                q[r] = 0.0f;
-        float total = 0.0f;
-        for (uint32_t j = 0; j < n; ++j)
-            total = __fadd_rn(total, q_at(j));
-        const int32_t draft = (mode == kModeVerify) ? draft_row : -1;
-        const uint32_t dm0 = __ballot_sync(full, draft >= 0 && lane < n && (int32_t)col[0] + id_off == draft);
-        const uint32_t dm1 = __ballot_sync(full, draft >= 0 && 32u + lane < n && (int32_t)col[1] + id_off == draft);
-        const uint32_t draft_idx = dm0 ? (uint32_t)__ffs((int)dm0) - 1u : (dm1 ? 31u + (uint32_t)__ffs((int)dm1) : 0xffffffffu);
-        const float q_draft = (dm0 | dm1) ? q_at(draft_idx) : 0.0f;
-        int32_t tok = -1, acc = 0;
-        float prob = 0.0f;
-        if (mode == kModeDistOnly) {
-            tok = (int32_t)col_at(0) + id_off;
-            prob = __fdiv_rn(q_at(0), total);
-        } else {
-            uint32_t skip_idx = 0xffffffffu;
-            float walk_total = total;
-            if (mode == kModeVerify) { // sampler.cpp:100-106
-                acc = __fmul_rn(u_row, total) < q_draft;
-                if (acc) {
-                    tok = draft;
-                    prob = __fdiv_rn(q_draft, total);
-                } else {
-                    skip_idx = draft_idx;
-                    walk_total = __fsub_rn(total, q_draft);
-                    if (n == 1 && draft_idx == 0u) { // nothing but the rejected draft
-                        tok = draft;
-                        prob = 1.0f;
-                    }
-                }
-            }
-            if (tok < 0) {
-                float r = __fmul_rn((mode == kModeVerify) ? u2_row : u_row, walk_total);
-                const float eps = 1e-6f * walk_total;
-                const uint32_t first_valid = (skip_idx == 0u) ? 1u : 0u;
-                const uint32_t last_valid = (skip_idx == n - 1u) ? n - 2u : n - 1u;
-                if (lane == skip_idx)
-                    q[0] = 0.0f; // the skipped draft never wins
-                if (32u + lane == skip_idx)
-                    q[1] = 0.0f;
-                uint32_t hit = last_valid; // rounding: the last candidate (sampler.cpp:72)
-                float q_hit = q_at(last_valid);
-                bool found = false;
-                for (uint32_t j = 0; j < n && !found; ++j) {
-                    const float qj = q_at(j);
-                    if (r < qj) {
-                        found = true;
-                        hit = j;
-                        q_hit = qj;
-                        // boundary below (not for the first candidate) or above (not for the last)
-                        if ((j != first_valid && r < eps) || (j < last_valid && __fsub_rn(qj, r) < eps))
-                            fl |= MK_FLAG_NEAR_CDF_BOUNDARY;
-                    } else {
-                        r = __fsub_rn(r, qj);
-                    }
-                }
-                tok = (int32_t)col_at(hit) + id_off;
-                prob = __fdiv_rn(q_hit, walk_total);
-            }
-        }
-        if (lane == 0) {
-            if (o.token) o.token[row] = tok;
-            if (o.prob) o.prob[row] = prob;
-            if (o.flags) o.flags[row] = fl;
-            if (o.n_cand) o.n_cand[row] = n;
-            if (o.accepted) o.accepted[row] = acc;
-            if (o.total_out) o.total_out[row] = total;
-            if (o.timing)
-                o.timing[(size_t)row * 64 + 3] = global_ns();
-        }
-        // the candidate list as the chains saw it, except that a rejected draft keeps its weight there
-#pragma unroll
-        for (uint32_t r = 0; r < 2; ++r) {
-            const uint32_t i = r * 32u + lane;
-            if (i < min(n, o.cand_cap)) {
-                const float qo = sorted ? __uint_as_float(~(uint32_t)(key[r] >> 32)) : __uint_as_float((uint32_t)(key[r] & 0xffffffffull));
-                if (o.cand_ids) o.cand_ids[(size_t)row * o.cand_cap + i] = (int32_t)col[r] + id_off;
-                if (o.cand_q) o.cand_q[(size_t)row * o.cand_cap + i] = qo;
-            }
+    for (uint32_t r = 0; r < 2; ++r) {
+        key[r] = ~0ull;
+        if (r * 32u + lane < n) {
+            const unsigned long long raw = fkeys[r * 32u + lane];
+            const float q = __uint_as_float((uint32_t)(raw >> 32));
+            const uint32_t col = (uint32_t)(raw & 0xffffffffull);
+            key[r] = sorted ? pack_by_weight(q, col) : pack_by_column(q, col);
         }
     }
+    for (uint32_t k = 2; k <= 64u; k <<= 1)
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            if (j == 32u) { // k == 64: element `lane` against element `lane + 32`, ascending
+                const unsigned long long lo = min(key[0], key[1]), hi = max(key[0], key[1]);
+                key[0] = lo;
+                key[1] = hi;
+            } else {
+#pragma unroll
+                for (uint32_t r = 0; r < 2; ++r) {
+                    const uint32_t i = r * 32u + lane;
+                    const unsigned long long other = __shfl_xor_sync(full, key[r], j);
+                    const bool keep_small = ((i & j) == 0) == ((i & k) == 0);
+                    key[r] = (keep_small == (key[r] < other)) ? key[r] : other;
+                }
+            }
+        }
+    float q[2];
+    uint32_t col[2];
+#pragma unroll
+    for (uint32_t r = 0; r < 2; ++r) {
+        if (sorted) {
+            q[r] = __uint_as_float(~(uint32_t)(key[r] >> 32));
+            col[r] = (uint32_t)(key[r] & 0xffffffffull);
+        } else {
+            q[r] = __uint_as_float((uint32_t)(key[r] & 0xffffffffull));
+            col[r] = (uint32_t)(key[r] >> 32);
+        }
+        if (r * 32u + lane >= n)
+            q[r] = 0.0f;
+    }
+    auto q_at = [&](uint32_t j) -> float { return __shfl_sync(full, j < 32u ? q[0] : q[1], (int)(j & 31u)); };
+    auto col_at = [&](uint32_t j) -> uint32_t { return __shfl_sync(full, j < 32u ? col[0] : col[1], (int)(j & 31u)); };
+    if (cut_k) { // sampler.cpp:40-42; the tie rule is the general finish's
+        const float qk = q_at(top_k - 1u);
+        const uint32_t edge_key = s.thr_topk_key;
+        const float below = key_to_float(edge_key - 1u);
+        if (edge_key > order_key(-FLT_MAX) && expf_host_exact(__fmul_rn(__fsub_rn(below, m), inv_t)) >= qk)
+            fl |= MK_FLAG_GUARD_BAND;
+        n = top_k;
+    }
+    if (use_topp) { // sampler.cpp:44-61, sequentially
+        double total_d = 0.0;
+        for (uint32_t j = 0; j < n; ++j)
+            total_d += (double)q_at(j);
+        const double band = 0x1p-40 * total_d, want = (double)top_p * total_d;
+        double run = 0.0, prev = 0.0;
+        uint32_t k = 0;
+        for (uint32_t j = 0; j < n && run < want; ++j) {
+            prev = run;
+            run += (double)q_at(j);
+            k = j + 1u;
+        }
+        if (k >= 1 && (fabs(run - want) <= band || (k >= 2 && fabs(prev - want) <= band)))
+            fl |= MK_FLAG_GUARD_BAND;
+        n = max(k, 1u);
+    }
+#pragma unroll
+    for (uint32_t r = 0; r < 2; ++r)
+        if (r * 32u + lane >= n)
+            q[r] = 0.0f;
+    float total = 0.0f;
+    for (uint32_t j = 0; j < n; ++j)
+        total = __fadd_rn(total, q_at(j));
+    const int32_t draft = (mode == kModeVerify) ? draft_row : -1;
+    const uint32_t dm0 = __ballot_sync(full, draft >= 0 && lane < n && (int32_t)col[0] + id_off == draft);
+    const uint32_t dm1 = __ballot_sync(full, draft >= 0 && 32u + lane < n && (int32_t)col[1] + id_off == draft);
+    const uint32_t draft_idx = dm0 ? (uint32_t)__ffs((int)dm0) - 1u : (dm1 ? 31u + (uint32_t)__ffs((int)dm1) : 0xffffffffu);
+    const float q_draft = (dm0 | dm1) ? q_at(draft_idx) : 0.0f;
+    int32_t tok = -1, acc = 0;
+    float prob = 0.0f;
+    if (mode == kModeDistOnly) {
+        tok = (int32_t)col_at(0) + id_off;
+        prob = __fdiv_rn(q_at(0), total);
+    } else {
+        uint32_t skip_idx = 0xffffffffu;
+        float walk_total = total;
+        if (mode == kModeVerify) { // sampler.cpp:100-106
+            acc = __fmul_rn(u_row, total) < q_draft;
+            if (acc) {
+                tok = draft;
+                prob = __fdiv_rn(q_draft, total);
+            } else {
+                skip_idx = draft_idx;
+                walk_total = __fsub_rn(total, q_draft);
+                if (n == 1 && draft_idx == 0u) { // nothing but the rejected draft
+                    tok = draft;
+                    prob = 1.0f;
+                }
+            }
+        }
+        if (tok < 0) {
+            float r = __fmul_rn((mode == kModeVerify) ? u2_row : u_row, walk_total);
+            const float eps = 1e-6f * walk_total;
+            const uint32_t first_valid = (skip_idx == 0u) ? 1u : 0u;
+            const uint32_t last_valid = (skip_idx == n - 1u) ? n - 2u : n - 1u;
+            if (lane == skip_idx)
+                q[0] = 0.0f; // the skipped draft never wins
+            if (32u + lane == skip_idx)
+                q[1] = 0.0f;
+            uint32_t hit = last_valid; // rounding: the last candidate (sampler.cpp:72)
+            float q_hit = q_at(last_valid);
+            bool found = false;
+            for (uint32_t j = 0; j < n && !found; ++j) {
+                const float qj = q_at(j);
+                if (r < qj) {
+                    found = true;
+                    hit = j;
+                    q_hit = qj;
+                    // boundary below (not for the first candidate) or above (not for the last)
+                    if ((j != first_valid && r < eps) || (j < last_valid && __fsub_rn(qj, r) < eps))
+                        fl |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                } else {
+                    r = __fsub_rn(r, qj);
+                }
+            }
+            tok = (int32_t)col_at(hit) + id_off;
+            prob = __fdiv_rn(q_hit, walk_total);
+        }
+    }
+    if (lane == 0) {
+        if (o.token) o.token[row] = tok;
+        if (o.prob) o.prob[row] = prob;
+        if (o.flags) o.flags[row] = fl;
+        if (o.n_cand) o.n_cand[row] = n;
+        if (o.accepted) o.accepted[row] = acc;
+        if (o.total_out) o.total_out[row] = total;
+        if (o.timing)
+            o.timing[(size_t)row * 64 + 3] = global_ns();
+    }
+    // the candidate list as the chains saw it, except that a rejected draft keeps its weight there
+#pragma unroll
+    for (uint32_t r = 0; r < 2; ++r) {
+        const uint32_t i = r * 32u + lane;
+        if (i < min(n, o.cand_cap)) {
+            const float qo = sorted ? __uint_as_float(~(uint32_t)(key[r] >> 32)) : __uint_as_float((uint32_t)(key[r] & 0xffffffffull));
+            if (o.cand_ids) o.cand_ids[(size_t)row * o.cand_cap + i] = (int32_t)col[r] + id_off;
+            if (o.cand_q) o.cand_q[(size_t)row * o.cand_cap + i] = qo;
+        }
+    }
+}
 
 } // namespace
 

@@ -175,8 +175,30 @@ def test_flat_rows_keep_long_sorted_lists(gpu_sampler_factory, ref, params):
         assert (tok[i], bool(acc[i])) == ref.verify(params, rows[i], int(draft[i]), u[i], u2[i]), f"row {i}"
 
 
+@pytest.mark.parametrize("params", [
+    SamplingParams(temperature=1.0, top_p=0.4),
+    SamplingParams(temperature=1.0, top_k=10000),
+    SamplingParams(temperature=1.0, top_k=11000, top_p=0.999),
+], ids=["topp", "topk", "topk_topp"])
+def test_lists_a_little_longer_than_the_on_chip_sort(gpu_sampler_factory, ref, params):
+    """A little over 8192 candidates: the list is merge-sorted through the row's scratch and still fits shared memory
+    for the sequential chains, which read it from there (longer lists stay in device memory): flat rows, one of them
+    with many exact ties in weight, element for element against the reference."""
+    v, b, cap = 40000, 4, 12000
+    rng = np.random.default_rng(19)
+    rows = rng.normal(0, 0.4, size=(b, v)).astype(np.float32)
+    rows[1] = np.round(rows[1] * 16) / 16        # exact ties in weight: order by id inside a tie
+    rows[2, 777] = 3.0
+    u = synth.uniforms(29, b)
+    res = gpu_rows(gpu_sampler_factory, rows, params, u, cap=cap)
+    want = [ref.sample(params, rows[i], u[i], cap=cap) for i in range(b)]
+    n_c = [w["n_cand"] for w in want]
+    assert max(n_c) > 8192 and min(n_c) < 11500, n_c
+    compare_sample(res, want, cap=cap)
+
+
 def test_second_pass_only_for_rows_that_ask(gpu_sampler_factory, ref):
-    """top_p alone: the first launch keeps the 256 largest elements per row; rows whose nucleus is longer stream a
+    """top_p alone: the first launch keeps the 24 largest elements per row; rows whose nucleus is longer stream a
     second time. Flat and peaked rows share a batch, with histories and a mask, and the same handle is then used for
     a batch in which no row asks for the second pass: marks left by one call must not leak into the next."""
     v, b, cap = 50021, 8, 4096
