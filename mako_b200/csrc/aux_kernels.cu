@@ -276,6 +276,152 @@ namespace {
 constexpr int kPqThreads = 512; // the sort of two long lists (a flat row: thousands of candidates each) is what takes the time
 }
 
+// The rejected position's resample when a list runs to hundreds or thousands of entries: no sort. Each list marks its
+// ids in a bitmap of the vocabulary; the number of marked ids before each word (a prefix popcount) makes an id's place
+// in ascending order one popcount away. The drafter's weights are laid out by that rank, every target entry looks its
+// id up in the drafter's bitmap and leaves max-able residual p/P - q/Q at its own rank, and one warp adds and walks the
+// residuals in ascending id as the restated rule demands. Shared memory: two bitmaps, two rank arrays, two float
+// arrays by rank.
+constexpr uint32_t kPqBitmapVocab = 163840, kPqBmWords = kPqBitmapVocab / 32, kPqRankMin = 256;
+constexpr size_t kPqRankSmem = 2 * (kPqBmWords * 4 + kPqBmWords * 2) + 2 * 4096 * 4;
+__device__ __noinline__ void pq_resolve_by_rank(const PqResolveArgs& a, uint32_t row, uint32_t np, uint32_t nq, float total_p,
+                                                float total_q, int32_t d, uint32_t fl)
+{
+    extern __shared__ unsigned long long pq_keys[];
+    __shared__ uint32_t s_wtot[2][kPqThreads / 32];
+    unsigned char* const base = reinterpret_cast<unsigned char*>(pq_keys);
+    uint32_t* const bm_p = reinterpret_cast<uint32_t*>(base);
+    uint32_t* const bm_q = bm_p + kPqBmWords;
+    uint16_t* const wp_p = reinterpret_cast<uint16_t*>(bm_q + kPqBmWords);
+    uint16_t* const wp_q = wp_p + kPqBmWords;
+    float* const res = reinterpret_cast<float*>(wp_q + kPqBmWords); // residuals of the target's entries, by rank
+    float* const qv = res + a.cap;                                    // the drafter's weights, by rank
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t words = (a.n_vocab + 31u) >> 5;
+    __syncthreads(); // the lists staged for the sort path are dead from here
+    for (uint32_t w = tid; w < 2u * kPqBmWords; w += kPqThreads)
+        bm_p[w] = 0u;
+    __syncthreads();
+    const int32_t* const pid = a.p_ids + (size_t)row * a.cap;
+    const int32_t* const qid = a.q_ids + (size_t)row * a.cap;
+    const float* const pw = a.p_q + (size_t)row * a.cap;
+    const float* const qw = a.q_q + (size_t)row * a.cap;
+    for (uint32_t i = tid; i < np; i += kPqThreads) {
+        const uint32_t c = (uint32_t)(pid[i] - a.id_offset);
+        atomicOr(&bm_p[c >> 5], 1u << (c & 31u));
+    }
+    for (uint32_t i = tid; i < nq; i += kPqThreads) {
+        const uint32_t c = (uint32_t)(qid[i] - a.id_offset);
+        atomicOr(&bm_q[c >> 5], 1u << (c & 31u));
+    }
+    __syncthreads();
+    // prefix popcounts of both bitmaps: each thread a run of words, a scan over the threads' sums
+    const uint32_t per = (words + kPqThreads - 1u) / kPqThreads, w0 = min(tid * per, words), w1 = min(w0 + per, words);
+    uint32_t mine_p = 0, mine_q = 0;
+    for (uint32_t w = w0; w < w1; ++w) {
+        mine_p += (uint32_t)__popc(bm_p[w]);
+        mine_q += (uint32_t)__popc(bm_q[w]);
+    }
+    uint32_t inc_p = mine_p, inc_q = mine_q;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t yp = __shfl_up_sync(0xffffffffu, inc_p, o), yq = __shfl_up_sync(0xffffffffu, inc_q, o);
+        if ((int)lane >= o) {
+            inc_p += yp;
+            inc_q += yq;
+        }
+    }
+    if (lane == 31) {
+        s_wtot[0][warp] = inc_p;
+        s_wtot[1][warp] = inc_q;
+    }
+    __syncthreads();
+    uint32_t before_p = inc_p - mine_p, before_q = inc_q - mine_q;
+    for (uint32_t w = 0; w < warp; ++w) {
+        before_p += s_wtot[0][w];
+        before_q += s_wtot[1][w];
+    }
+    for (uint32_t w = w0; w < w1; ++w) {
+        wp_p[w] = (uint16_t)before_p;
+        wp_q[w] = (uint16_t)before_q;
+        before_p += (uint32_t)__popc(bm_p[w]);
+        before_q += (uint32_t)__popc(bm_q[w]);
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < nq; i += kPqThreads) {
+        const uint32_t c = (uint32_t)(qid[i] - a.id_offset);
+        qv[wp_q[c >> 5] + __popc(bm_q[c >> 5] & ((1u << (c & 31u)) - 1u))] = qw[i];
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < np; i += kPqThreads) {
+        const uint32_t c = (uint32_t)(pid[i] - a.id_offset), bit = 1u << (c & 31u);
+        const float pn = __fdiv_rn(pw[i], total_p);
+        float qn = 0.0f;
+        if (bm_q[c >> 5] & bit)
+            qn = __fdiv_rn(qv[wp_q[c >> 5] + __popc(bm_q[c >> 5] & (bit - 1u))], total_q);
+        res[wp_p[c >> 5] + __popc(bm_p[c >> 5] & (bit - 1u))] = __fsub_rn(pn, qn);
+    }
+    __syncthreads();
+    if (tid < 32) {
+        const uint32_t full = 0xffffffffu;
+        float total_r = 0.0f;
+        uint32_t n_res = 0;
+        for (uint32_t base_i = 0; base_i < np; base_i += 32u) {
+            const float r_l = (base_i + lane < np) ? res[base_i + lane] : 0.0f;
+            const int cnt = (int)min(32u, np - base_i);
+            for (int j = 0; j < cnt; ++j) {
+                const float rj = __shfl_sync(full, r_l, j);
+                if (rj > 0.0f) {
+                    total_r = __fadd_rn(total_r, rj);
+                    ++n_res;
+                }
+            }
+        }
+        float r = __fmul_rn(a.u_resample[row], total_r);
+        uint32_t hit = 0xffffffffu, last = 0xffffffffu; // ranks
+        bool done = false;
+        for (uint32_t base_i = 0; base_i < np && !done; base_i += 32u) {
+            const float r_l = (base_i + lane < np) ? res[base_i + lane] : 0.0f;
+            const int cnt = (int)min(32u, np - base_i);
+            for (int j = 0; j < cnt && !done; ++j) {
+                const float rj = __shfl_sync(full, r_l, j);
+                if (rj > 0.0f) {
+                    last = base_i + (uint32_t)j;
+                    if (r < rj) {
+                        hit = last;
+                        done = true;
+                    } else {
+                        r = __fsub_rn(r, rj);
+                    }
+                }
+            }
+        }
+        if (!done)
+            hit = last;
+        if (lane == 0) {
+            int32_t tok = d;
+            if (n_res && hit != 0xffffffffu) {
+                // the id of rank `hit`: the last word whose prefix does not exceed it, then its (hit - prefix)-th bit
+                uint32_t lo = 0, hi = words;
+                while (hi - lo > 1u) {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if ((uint32_t)wp_p[mid] <= hit)
+                        lo = mid;
+                    else
+                        hi = mid;
+                }
+                uint32_t bits = bm_p[lo];
+                for (uint32_t k = hit - wp_p[lo]; k > 0u; --k)
+                    bits &= bits - 1u;
+                tok = (int32_t)(lo * 32u + (uint32_t)(__ffs((int)bits) - 1)) + a.id_offset;
+            }
+            a.accepted[row] = 0;
+            a.token[row] = tok;
+            if (a.flags) a.flags[row] = fl;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kPqThreads) pq_resolve_kernel(const PqResolveArgs a)
 {
     extern __shared__ unsigned long long pq_keys[]; // [2][cap2]
@@ -334,6 +480,10 @@ __global__ void __launch_bounds__(kPqThreads) pq_resolve_kernel(const PqResolveA
             a.token[row] = d;
             if (a.flags) a.flags[row] = fl;
         }
+        return;
+    }
+    if (a.n_vocab <= kPqBitmapVocab && a.cap <= 4096u && max(np, nq) > kPqRankMin) {
+        pq_resolve_by_rank(a, row, np, nq, total_p, total_q, d, fl);
         return;
     }
     // sort both lists by id
@@ -432,7 +582,9 @@ cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream)
     uint32_t cap2 = 2;
     while (cap2 < a.cap)
         cap2 <<= 1;
-    const size_t smem = 2 * (size_t)cap2 * 8;
+    size_t smem = 2 * (size_t)cap2 * 8;
+    if (a.n_vocab <= kPqBitmapVocab && a.cap <= 4096 && smem < kPqRankSmem)
+        smem = kPqRankSmem;
     static bool configured[64] = {}; // the attribute is per device
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

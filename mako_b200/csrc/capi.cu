@@ -504,6 +504,7 @@ int mk_sampler_verify_pq_batch(mk_sampler* s, const mk_rows* rows, const float* 
     r.draft_token = draft_token;
     r.u_accept = u_accept; r.u_resample = u_resample;
     r.accepted = accepted; r.token = token; r.flags = flags;
+    r.n_vocab = rows->n_vocab; r.id_offset = rows->id_offset;
     MK_CUDA(mk::launch_pq_resolve(r, st));
     return MK_OK;
 }

@@ -101,6 +101,7 @@ struct PqResolveArgs {
     const int32_t* draft_token; // drawn from q by the sample launch
     const float* u_accept; const float* u_resample;
     int32_t* accepted; int32_t* token; uint32_t* flags;
+    uint32_t n_vocab; int32_t id_offset; // ids are id_offset .. id_offset + n_vocab - 1
 };
 cudaError_t launch_pq_resolve(const PqResolveArgs& a, cudaStream_t stream);
 

@@ -40,6 +40,32 @@ def test_verify_deterministic_draft(gpu_sampler_factory, ref, params):
     assert 0 < n_acc < b
 
 
+def test_verify_pq_with_lists_of_thousands(gpu_sampler_factory, ref):
+    """Rows without spikes: the target keeps thousands of candidates, so a rejected position's resample runs over long
+    lists (ranked through bitmaps instead of sorted); draft token, acceptance and returned token against the
+    restatement, and some positions must be rejected."""
+    import torch
+    v, b = 129280, 12
+    params = SamplingParams(temperature=0.55, top_p=0.9)      # 1300 to 2500 target candidates, up to 300 drafter's
+    inp = Inputs(4242, b, v, n_spikes=0, sigma=2.0)
+    lq = synth.add_noise(4242, inp.logits, v, sigma=1.0)
+    g = inp.to_gpu()
+    s = gpu_sampler_factory(v, b, 16)
+    res = s.verify_pq(g["logits"], torch.from_numpy(lq).cuda(), params, g["u"], g["u2"], g["u3"])
+    torch.cuda.synchronize()
+    d, acc, tok = res.draft_token.cpu().numpy(), res.accepted.cpu().numpy(), res.token.cpu().numpy()
+    flags = res.flags.cpu().numpy()
+    n_rej = 0
+    for i in range(b):
+        wd, wa, wt = ref.verify_pq(params, inp.logits[i], lq[i], inp.u[i], inp.u2[i], inp.u3[i])
+        assert not (flags[i] & 0x50), f"row {i} flags {flags[i]:#x}"
+        if flags[i] & 0x2:
+            continue
+        assert (d[i], bool(acc[i]), tok[i]) == (wd, wa, wt), f"row {i}"
+        n_rej += not wa
+    assert n_rej >= 3
+
+
 def test_verify_pq_config3(gpu_sampler_factory, ref):
     """64 sequences x 5 positions in the benchmark; here 24 positions with the same distributions."""
     import torch
