@@ -164,7 +164,10 @@ __global__ void __launch_bounds__(kMergeThreadsFew) vp_merge_kernel(const VpMerg
     if (n > 1)
         sort_keys(keys, n2, n_thr);
 
-    if (tid == 0) {
+    // The rest is sequential by the reference's definition (double sums for top_p, a float total, the walk) or tiny:
+    // one warp runs it, the candidates handed round 32 at a time by shuffles so that no chain waits for a load.
+    if (tid < 32) {
+        const uint32_t lane = tid, full = 0xffffffffu;
         auto q_at = [&](uint32_t i) -> float {
             const unsigned long long key = keys[i];
             return sorted ? __uint_as_float(~(uint32_t)(key >> 32)) : __uint_as_float((uint32_t)(key & 0xffffffffull));
@@ -173,7 +176,6 @@ __global__ void __launch_bounds__(kMergeThreadsFew) vp_merge_kernel(const VpMerg
             const unsigned long long key = keys[i];
             return sorted ? (uint32_t)(key & 0xffffffffull) : (uint32_t)(key >> 32);
         };
-        auto id_at = [&](uint32_t i) -> uint32_t { return tag_at(i) & kIdMask; };
         // A shard whose whole list is inside the deciding set may hold further members the merge cannot see.
         uint32_t n_decide = n; // the set whose completeness matters: all candidates when the total is their sum
         if (cut_k)
@@ -182,24 +184,41 @@ __global__ void __launch_bounds__(kMergeThreadsFew) vp_merge_kernel(const VpMerg
             double total = 0.0, band;
             if (need_sum && !(flags & MK_FLAG_NO_CANDIDATE)) {
                 const double c2 = (double)inv_t * 1.4426950408889634;
-                for (uint32_t g = 0; g < a.n_shards; ++g) {
-                    const float mg = s_max[g];
-                    const double sg = s_sum[g];
-                    if (mg > ninf && sg > 0.0)
-                        total += sg * exp2((double)(mg - m) * c2);
+                for (uint32_t g0 = 0; g0 < a.n_shards; g0 += 32u) { // the shards' rescaled sums, added in shard order
+                    const uint32_t g = g0 + lane;
+                    double term = 0.0;
+                    if (g < a.n_shards && s_max[g] > ninf && s_sum[g] > 0.0)
+                        term = s_sum[g] * exp2((double)(s_max[g] - m) * c2);
+                    const int cnt = (int)min(32u, a.n_shards - g0);
+                    for (int j = 0; j < cnt; ++j)
+                        total += __shfl_sync(full, term, j);
                 }
                 band = 1e-5 * total;
             } else {
-                for (uint32_t i = 0; i < n; ++i)
-                    total += (double)q_at(i);
+                for (uint32_t base = 0; base < n; base += 32u) {
+                    const float q = (base + lane < n) ? q_at(base + lane) : 0.0f;
+                    const int cnt = (int)min(32u, n - base);
+                    for (int j = 0; j < cnt; ++j)
+                        total += (double)__shfl_sync(full, q, j);
+                }
                 band = 0x1p-40 * total;
             }
             const double want = (double)prm.top_p * total;
             double run = 0.0, prev = 0.0;
             uint32_t k = 0;
-            while (k < n && run < want) {
-                prev = run;
-                run += (double)q_at(k++);
+            bool open = true;
+            for (uint32_t base = 0; base < n && open; base += 32u) {
+                const float q = (base + lane < n) ? q_at(base + lane) : 0.0f;
+                const int cnt = (int)min(32u, n - base);
+                for (int j = 0; j < cnt; ++j) {
+                    const double qj = (double)__shfl_sync(full, q, j);
+                    open = open && run < want;
+                    if (open) {
+                        prev = run;
+                        run += qj;
+                        k = base + (uint32_t)j + 1u;
+                    }
+                }
             }
             if (need_sum && run < want)
                 flags |= MK_FLAG_VP_TRUNCATED;
@@ -214,38 +233,54 @@ __global__ void __launch_bounds__(kMergeThreadsFew) vp_merge_kernel(const VpMerg
         else if (cut_k)
             n_decide = min(n_decide, prm.top_k);
         // count members per shard among the deciding set
-        for (uint32_t i = 0; i < n_decide; ++i)
-            s_shard_in[tag_at(i) >> kShardShift] += 1;
-        for (uint32_t g = 0; g < a.n_shards && g < 64; ++g) {
+        for (uint32_t i = lane; i < n_decide; i += 32u)
+            atomicAdd(&s_shard_in[tag_at(i) >> kShardShift], 1u);
+        __syncwarp();
+        bool cut_short = false;
+        for (uint32_t g = lane; g < a.n_shards && g < 64u; g += 32u) {
             const uint32_t hdr = s_hdr[g];
             const uint32_t ng = hdr & 0xffffu;
             const bool more = (hdr & 0x40000000u) != 0;
-            if ((hdr & 0x80000000u) || (more && ng > 0 && s_shard_in[g] >= ng))
-                flags |= MK_FLAG_VP_TRUNCATED;
+            cut_short = cut_short || (hdr & 0x80000000u) || (more && ng > 0 && s_shard_in[g] >= ng);
         }
+        if (__any_sync(full, cut_short))
+            flags |= MK_FLAG_VP_TRUNCATED;
         float total = 0.0f;
-        for (uint32_t i = 0; i < n; ++i)
-            total = __fadd_rn(total, q_at(i));
+        for (uint32_t base = 0; base < n; base += 32u) {
+            const float q = (base + lane < n) ? q_at(base + lane) : 0.0f;
+            const int cnt = (int)min(32u, n - base);
+            for (int j = 0; j < cnt; ++j)
+                total = __fadd_rn(total, __shfl_sync(full, q, j));
+        }
         float r = __fmul_rn(a.u[row], total);
         const float eps = 1e-6f * total;
-        int32_t tok = (int32_t)id_at(n - 1);
-        float prob = __fdiv_rn(q_at(n - 1), total);
-        for (uint32_t i = 0; i < n; ++i) {
-            const float q = q_at(i);
-            if (r < q) {
-                tok = (int32_t)id_at(i);
-                prob = __fdiv_rn(q, total);
-                if ((i > 0 && r < eps) || (i + 1 < n && __fsub_rn(q, r) < eps))
-                    flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
-                break;
+        uint32_t hit = n - 1u;
+        float q_hit = q_at(n - 1u);
+        bool found = false;
+        for (uint32_t base = 0; base < n && !found; base += 32u) {
+            const float q = (base + lane < n) ? q_at(base + lane) : 0.0f;
+            const int cnt = (int)min(32u, n - base);
+            for (int j = 0; j < cnt && !found; ++j) {
+                const float qj = __shfl_sync(full, q, j);
+                const uint32_t i = base + (uint32_t)j;
+                if (r < qj) {
+                    found = true;
+                    hit = i;
+                    q_hit = qj;
+                    if ((i > 0 && r < eps) || (i + 1 < n && __fsub_rn(qj, r) < eps))
+                        flags |= MK_FLAG_NEAR_CDF_BOUNDARY;
+                } else {
+                    r = __fsub_rn(r, qj);
+                }
             }
-            r = __fsub_rn(r, q);
         }
-        if (a.token) a.token[row] = tok;
-        if (a.prob) a.prob[row] = prob;
-        if (a.flags) a.flags[row] = flags;
-        if (a.n_cand) a.n_cand[row] = n;
-        s_nfinal = n;
+        if (lane == 0) {
+            if (a.token) a.token[row] = (int32_t)(tag_at(hit) & kIdMask);
+            if (a.prob) a.prob[row] = __fdiv_rn(q_hit, total);
+            if (a.flags) a.flags[row] = flags;
+            if (a.n_cand) a.n_cand[row] = n;
+            s_nfinal = n;
+        }
     }
     __syncthreads();
     if (a.cand_ids || a.cand_q) {
