@@ -43,9 +43,12 @@ def _cpu_round(ref, p, logits, drafts, forced, u, hist):
     (SamplingParams(temperature=0.7, top_k=40, top_p=0.95, repetition_penalty=1.3), True),
     (SamplingParams(temperature=0.0), True),
 ], ids=["penalised", "nucleus+forced", "greedy+forced"])
-def test_rounds_of_four_drafts_and_a_bonus_row(gpu_sampler_factory, ref, params, with_forced):
+@pytest.mark.parametrize("v,n_seq", [(40003, 64), (129280, 24)], ids=["ragged_rows", "aligned_rows"])
+def test_rounds_of_four_drafts_and_a_bonus_row(gpu_sampler_factory, ref, params, with_forced, v, n_seq):
+    """Rows of 40003 columns are not 16-byte aligned and take the kernel's plain-load path, rows of 129280 columns
+    the bulk-copy path: the round's bookkeeping is the same on both."""
     import torch
-    v, n_seq, n_drafts, cap, rounds = 40003, 64, 4, 256, 3
+    n_drafts, cap, rounds = 4, 256, 3
     n_pos = n_drafts + 1
     s = gpu_sampler_factory(v, n_seq * n_pos)
     rng = np.random.default_rng(77)
