@@ -61,7 +61,8 @@ typedef struct mk_bias {
 
 /* A batch of rows. Row b reads logits + b*ld (n_vocab floats), history + b*history_ld, mask + b*mask_ld (words),
  * bias + b*n_bias. The fast (bulk-copy) path needs logits 16-byte aligned and ld % 4 == 0; other layouts take a
- * slower path with identical results. */
+ * slower path with identical results (about ten times the time per row: pad the rows to a multiple of four columns
+ * and keep the buffer 16-byte aligned). */
 typedef struct mk_rows {
     const float* logits;         /* device [batch][ld] fp32 — the row Sampler::sample is handed (sampler.hpp:27) */
     uint64_t ld;
