@@ -19,15 +19,18 @@
 //                 then the n-th set bit of the word) — and release it to the readers.
 //   warps 3-10    readers: 128-bit shared loads, allowed-token mask, running row maximum (warp shuffles), and
 //                 collection of every element that can still become a candidate: the keep thresholds of min_p,
-//                 top_k and top_p are all lower-bounded by a function of the running maximum (or of a histogram of
-//                 order-preserving float keys for top_k) that only rises while the row streams, so filtering with
-//                 the current bound keeps a superset of the final candidates. The loop exists in four variants.
-//   all warps     finish: exact weights q = expf((l - max) * inv_t) for the few collected elements with the host
-//                 library's float exponential (device_expf.cuh), min_p, top_k, top_p, and the sequential float
-//                 total and walk of the draw — in the reference's precision and order, because token ids depend on
-//                 both. Steps only unusual rows need (long lists) live in functions of their own.
-//   second pass   top_p alone: the first launch keeps the 256 largest elements; a row whose nucleus that does not
+//                 top_k and top_p are all lower-bounded by a function of the running maximum (or, for top_k, of a
+//                 histogram of the reader threads' maxima) that only rises while the row streams, so filtering with
+//                 the current bound keeps a superset of the final candidates. The loop exists in five variants.
+//   finish        exact weights q = expf((l - max) * inv_t) for the few collected elements with the host library's
+//                 float exponential (device_expf.cuh), min_p, top_k, top_p, and the sequential float total and walk
+//                 of the draw — in the reference's precision and order, because token ids depend on both. Up to 64
+//                 candidates: one warp, in registers. Steps only unusual rows need (long lists) live in functions of
+//                 their own.
+//   second pass   top_p alone: the first launch keeps the 24 largest elements; a row whose nucleus that does not
 //                 settle marks itself, and a second launch of this kernel streams the marked rows again.
+//   split launch  a few rows under a top_k: a second grid dimension over column shards, each CTA writing a shard
+//                 record for the merge kernel (also the local step of vocab-parallel sampling).
 //
 // Numeric contract (what makes ids bit-exact): IEEE division and no FMA contraction in the penalties and in
 // (l - max) * inv_t; q through expf_host_exact; top_p sums in double; total and the walk in float, left to right.
