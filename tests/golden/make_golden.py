@@ -26,6 +26,8 @@ CASES = [
     dict(temperature=0.6, top_p=0.95),
     dict(temperature=0.0),
     dict(temperature=1.3, top_k=5, repetition_penalty=1.5, presence_penalty=-0.2),
+    dict(temperature=1.0, top_k=50),                 # top_k alone, truncating: the list in canonical (sorted) order
+    dict(temperature=2.5, top_k=200, min_p=0.018),   # fewer candidates than top_k: nothing reordered, ascending id
 ]
 
 
